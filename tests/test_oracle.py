@@ -1,0 +1,93 @@
+"""The CPU oracle against the reference's own outputs and against the fp64 definition.
+
+Golden ``.npz`` files were produced by ``tests/golden/make_golden.py`` from the
+unmodified reference ``SSDLayer._ssd_core`` (``workloads/mamba/model_ref.py:123-162``).
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import ssd_oracle as O
+
+CORE_CASES = ["core_n16_q64", "core_n128_q64_slow", "core_n64_grouped_q32", "core_n128_q128_dt"]
+
+
+def _load(golden_dir, name):
+    z = np.load(golden_dir / f"{name}.npz")
+    d = {k: torch.from_numpy(z[k]) for k in z.files if k != "chunk"}
+    d["chunk"] = int(z["chunk"])
+    return d
+
+
+@pytest.mark.parametrize("name", CORE_CASES)
+def test_chunked_oracle_is_bit_identical_to_reference_fp16(golden_dir, name):
+    d = _load(golden_dir, name)
+    Y = O.ssd_chunked(d["X"], d["A"], d["B"], d["C"], d["chunk"], dt=d.get("dt"), dtype=torch.float16)
+    assert Y.dtype == torch.float16
+    assert torch.equal(Y, d["Y"])
+
+
+@pytest.mark.parametrize("name", CORE_CASES)
+def test_recurrence_agrees_with_reference_within_fp16_rounding(golden_dir, name):
+    d = _load(golden_dir, name)
+    Y = O.ssd_recurrence(d["X"], d["A"], d["B"], d["C"], dt=d.get("dt"))
+    per_bh, fro = O.error_metrics(d["Y"], Y)
+    assert per_bh < 5e-3 and fro < 2e-3, (per_bh, fro)
+
+
+def test_chunked_fp64_equals_recurrence():
+    inp = O.make_inputs(b=2, s=96, h=4, p=8, n=12, g=2, dtype=torch.float64, init=True, seed=3, decay_scale=0.3)
+    Yc, Hc = O.ssd_chunked(inp["X"], inp["A"], inp["B"], inp["C"], 32, initial_states=inp["initial_states"],
+                           dtype=torch.float64, return_final_state=True)
+    Yr, Hr = O.ssd_recurrence(inp["X"], inp["A"], inp["B"], inp["C"], initial_states=inp["initial_states"],
+                              return_final_state=True)
+    assert O.error_metrics(Yc, Yr)[0] < 1e-12
+    assert (Hc - Hr).abs().max() / Hr.abs().max() < 1e-12
+
+
+def test_chunk_length_independence_fp64():
+    inp = O.make_inputs(b=1, s=128, h=2, p=4, n=6, g=1, dtype=torch.float64, seed=4, decay_scale=0.1)
+    Y16 = O.ssd_chunked(inp["X"], inp["A"], inp["B"], inp["C"], 16, dtype=torch.float64)
+    Y64 = O.ssd_chunked(inp["X"], inp["A"], inp["B"], inp["C"], 64, dtype=torch.float64)
+    assert O.error_metrics(Y16, Y64)[0] < 1e-12
+
+
+def test_config0_fp32_within_1e4_of_definition():
+    cfg = dict(O.CONFIGS["cfg0"])
+    inp = O.make_inputs(seed=0, **cfg)
+    Y = O.ssd_chunked(inp["X"], inp["A"], inp["B"], inp["C"], cfg["chunk"], dtype=torch.float32)
+    Yr = O.ssd_recurrence(inp["X"], inp["A"], inp["B"], inp["C"])
+    per_bh, fro = O.error_metrics(Y, Yr)
+    assert per_bh < 1e-4 and fro < 1e-4, (per_bh, fro)
+
+
+def test_rejects_ragged_sequence_and_bad_groups():
+    inp = O.make_inputs(b=1, s=48, h=4, p=4, n=4, g=2, dtype=torch.float32, seed=1)
+    with pytest.raises(ValueError):
+        O.ssd_chunked(inp["X"], inp["A"], inp["B"], inp["C"], 32)
+    bad = O.make_inputs(b=1, s=32, h=4, p=4, n=4, g=3, dtype=torch.float32, seed=1)
+    with pytest.raises(ValueError):
+        O.ssd_chunked(bad["X"], bad["A"], bad["B"], bad["C"], 32)
+
+
+def test_sequence_shard_fold_reproduces_unsharded_state():
+    R = 4
+    inp = O.make_inputs(b=2, s=64 * R, h=3, p=4, n=5, g=1, dtype=torch.float64, init=True, seed=5, decay_scale=0.02)
+    _, Hfull = O.ssd_recurrence(inp["X"], inp["A"], inp["B"], inp["C"], initial_states=inp["initial_states"],
+                                return_final_state=True)
+    Yfull = O.ssd_recurrence(inp["X"], inp["A"], inp["B"], inp["C"], initial_states=inp["initial_states"])
+    finals, lds = [], []
+    for r in range(R):
+        sl = slice(64 * r, 64 * (r + 1))
+        _, F = O.ssd_recurrence(inp["X"][:, sl], inp["A"][:, sl], inp["B"][:, sl], inp["C"][:, sl],
+                                return_final_state=True)
+        finals.append(F)
+        lds.append(O.total_logdecay(inp["A"][:, sl]))
+    finals, lds = torch.stack(finals), torch.stack(lds)
+    for r in range(R):
+        sl = slice(64 * r, 64 * (r + 1))
+        Hin = O.fold_incoming_state(finals, lds, r, initial=inp["initial_states"])
+        Yr = O.ssd_recurrence(inp["X"][:, sl], inp["A"][:, sl], inp["B"][:, sl], inp["C"][:, sl], initial_states=Hin)
+        assert O.error_metrics(Yr, Yfull[:, sl])[0] < 1e-12
+    Hend = O.fold_incoming_state(finals, lds, R, initial=inp["initial_states"])
+    assert (Hend - Hfull).abs().max() / Hfull.abs().max() < 1e-12
