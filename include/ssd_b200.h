@@ -1,0 +1,144 @@
+/*
+ * ssd_b200 -- C ABI of the B200 (sm_100a) Mamba-2 SSD chunked-scan forward.
+ *
+ * The reference project (ShouyangDong/WorkloadSuite) is pure Python/PyTorch and
+ * has no FFI; the interface each entry point stands in for is therefore a Python
+ * call site of the `mamba` workload, cited per function as file:line within the
+ * reference checkout.
+ *
+ * Conventions
+ *   - every pointer in SsdArgs is a DEVICE pointer owned by the caller; the
+ *     library allocates nothing and keeps no state between calls (the one
+ *     exception is documented at its declaration);
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*); no entry
+ *     point synchronises the host with the device unless it says so;
+ *   - every function returns SSD_OK (0) or a negative SSD_ERR_* code; nothing is
+ *     thrown across the boundary and the process is never terminated;
+ *   - asynchronous device-side problems (a bounded wait that ran out) are written
+ *     to the int32 `status` word, to be read by the caller after the stream has
+ *     been synchronised (0 = fine).
+ */
+#ifndef SSD_B200_H_
+#define SSD_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  SSD_OK = 0,
+  SSD_ERR_NULL_POINTER = -1,
+  SSD_ERR_BAD_SHAPE = -2,      /* non-positive size, heads not divisible by groups */
+  SSD_ERR_BAD_CHUNK = -3,      /* seqlen not a multiple of chunk (reference: EinopsError at model_ref.py:106) */
+  SSD_ERR_UNSUPPORTED = -4,    /* shape/dtype/stride outside what the kernels cover */
+  SSD_ERR_WORKSPACE = -5,      /* workspace missing or smaller than ssd_b200_workspace_bytes() */
+  SSD_ERR_CUDA = -6,           /* a CUDA runtime call failed (launch, attribute) */
+  SSD_ERR_MISALIGNED = -7,     /* pointer or stride not aligned as the chosen kernel needs */
+  SSD_ERR_TOO_LARGE = -8       /* size beyond a stated fixed limit */
+};
+
+enum { SSD_DTYPE_F32 = 0, SSD_DTYPE_F16 = 1, SSD_DTYPE_BF16 = 2 };
+
+/* kernel selection */
+enum {
+  SSD_KERNEL_AUTO = 0,    /* tensor-core kernel when the shape allows, else the fp32 scan */
+  SSD_KERNEL_SCAN_F32 = 1,/* fp32 token recurrence on CUDA cores (any dtype in, fp32 math) */
+  SSD_KERNEL_TCGEN05 = 2  /* tcgen05/TMEM chunked kernel (f16/bf16 only) */
+};
+
+/* flags */
+enum {
+  SSD_FLAG_STATE_ONLY = 1 /* do not compute/write Y; only final_state / final_logdecay */
+};
+
+/*
+ * Arguments of one SSD forward.  Mirrors the tensor arguments of
+ *   SSDLayer._ssd_core(X_b, B_b, C_b, dt_b, A_dt_b, batch)   model_ref.py:123-131
+ * with the chunk axis folded back into the sequence axis, B/C left un-broadcast
+ * ([b,s,g,n]; head j reads group j / (nheads/ngroups), the rule of
+ * model_ref.py:97-99) and the zero initial carry of model_ref.py:153 made an
+ * optional input.  Strides are in ELEMENTS; the innermost axis (p or n) must
+ * have stride 1.
+ */
+typedef struct SsdArgs {
+  const void*  X;               /* [b,s,h,p]  dtype          model_ref.py:125 */
+  const float* A;               /* [b,s,h]    fp32 per-token log-decay (A_dt) :129 */
+  const void*  B;               /* [b,s,g,n]  dtype          :126 */
+  const void*  C;               /* [b,s,g,n]  dtype          :127 */
+  const void*  dt;              /* [b,s,h]    dtype, or NULL for dt == 1   :128,144 */
+  const float* initial_state;   /* [b,h,n,p]  fp32 contiguous, or NULL for zeros :153 */
+  void*        Y;               /* [b,s,h,p]  dtype          :162 (NULL allowed with SSD_FLAG_STATE_ONLY) */
+  float*       final_state;     /* [b,h,n,p]  fp32 contiguous, or NULL (the carry after the last chunk, :156) */
+  float*       final_logdecay;  /* [b,h]      fp32 sum of A over the sequence, or NULL */
+  void*        workspace;       /* >= ssd_b200_workspace_bytes() bytes, 256-byte aligned; may be NULL if that is 0 */
+  size_t       workspace_bytes;
+  int32_t*     status;          /* device int32, or NULL */
+  int32_t batch, seqlen, nheads, headdim, dstate, ngroups;
+  int32_t chunk;                /* the reference's block_len; seqlen % chunk must be 0 */
+  int32_t dtype;                /* SSD_DTYPE_* of X, B, C, dt, Y */
+  int32_t kernel;               /* SSD_KERNEL_* */
+  int32_t flags;                /* SSD_FLAG_* */
+  int32_t nsegments;            /* 0 = choose; >0 = split each sequence into this many independently
+                                   scanned segments joined by a state fold (needs workspace) */
+  int32_t reserved0;
+  int64_t x_stride[3];          /* b, s, h */
+  int64_t a_stride[3];          /* b, s, h */
+  int64_t b_stride[3];          /* b, s, g */
+  int64_t c_stride[3];          /* b, s, g */
+  int64_t dt_stride[3];         /* b, s, h */
+  int64_t y_stride[3];          /* b, s, h */
+} SsdArgs;
+
+/* Library/ABI version (bumped when SsdArgs changes). */
+int ssd_b200_abi_version(void);
+
+/* Text for an SSD_ERR_* code (static storage). */
+const char* ssd_b200_strerror(int code);
+
+/* Scratch bytes ssd_b200_forward() needs for these arguments (0 when the
+ * sequence is not split).  Returns 0 for invalid arguments; ssd_b200_forward
+ * reports the error.  No reference counterpart (the reference lets PyTorch
+ * allocate its temporaries at model_ref.py:135-161). */
+size_t ssd_b200_workspace_bytes(const SsdArgs* args);
+
+/* Name of the kernel family SSD_KERNEL_AUTO resolves to for these arguments
+ * ("scan_f32", "tcgen05") or "invalid". */
+const char* ssd_b200_kernel_name(const SsdArgs* args);
+
+/* The SSD forward: replaces SSDLayer._ssd_core, model_ref.py:123-162
+ * (in-chunk prefix sum :135, decay mask :139-141, C.B^T :143, Y_diag :145,
+ * chunk states :148-150, inter-chunk recurrence :152-157, Y_off :160-161,
+ * sum :162), plus the GQA broadcast of :97-99 and the X*dt product of :144. */
+int ssd_b200_forward(const SsdArgs* args, void* stream);
+
+/* Fold per-shard results of a sequence-sharded scan into the state entering one
+ * shard.  Shard q's zero-start final state is the fp32 block
+ * states + q*states_shard_stride, laid out [units][np]; its summed log-decay is
+ * logdecay + q*logdecay_shard_stride, laid out [units] (strides in floats, so
+ * both may live in one all-gather buffer); initial is [units][np] or NULL.
+ * Writes H_in(rank) = fold_{q<rank}(H <- exp(D_q) H + F_q) to out [units][np].
+ * rank may equal nshards (state after the last shard).  The reference has no
+ * sharded path; this is the linear-recurrence identity behind
+ * model_ref.py:152-157 applied across shards. */
+int ssd_b200_fold_states(const float* states, int64_t states_shard_stride, const float* logdecay,
+                         int64_t logdecay_shard_stride, const float* initial, float* out, int32_t nshards,
+                         int32_t rank, int64_t units, int64_t np, void* stream);
+
+/* Whole forward with HOST buffers: copies X/A/B/C (and dt, initial_state when
+ * given) from host memory, runs the forward and copies Y (and final_state) back,
+ * pipelined over batch slices on internal streams.  Every pointer in `host` is a
+ * host pointer (pinned memory gives the best rate), tensors contiguous; strides
+ * in `host` are ignored.  `dev_scratch` is a caller-owned DEVICE buffer of at
+ * least ssd_b200_host_scratch_bytes() bytes.  Synchronises the host before
+ * returning.  Stands in for calling the reference module with CPU tensors
+ * (bench.py:217-233 builds inputs on the default device and calls Model). */
+size_t ssd_b200_host_scratch_bytes(const SsdArgs* host);
+int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scratch_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SSD_B200_H_ */

@@ -1,0 +1,215 @@
+// C ABI of the SSD forward (declared in include/ssd_b200.h): argument
+// validation, kernel choice, sequence segmentation and the host-buffer pipeline.
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+
+#include "ssd_common.cuh"
+
+namespace {
+
+constexpr int kAbiVersion = 1;
+constexpr int kSmCount = 148;  // B200
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+int elem_size(int dtype) { return dtype == SSD_DTYPE_F32 ? 4 : 2; }
+
+int validate(const SsdArgs* a) {
+  if (!a) return SSD_ERR_NULL_POINTER;
+  if (a->batch <= 0 || a->seqlen <= 0 || a->nheads <= 0 || a->headdim <= 0 || a->dstate <= 0 || a->ngroups <= 0)
+    return SSD_ERR_BAD_SHAPE;
+  if (a->nheads % a->ngroups != 0) return SSD_ERR_BAD_SHAPE;
+  if (a->chunk <= 0 || a->seqlen % a->chunk != 0) return SSD_ERR_BAD_CHUNK;
+  if (a->dtype != SSD_DTYPE_F32 && a->dtype != SSD_DTYPE_F16 && a->dtype != SSD_DTYPE_BF16)
+    return SSD_ERR_UNSUPPORTED;
+  if (a->kernel != SSD_KERNEL_AUTO && a->kernel != SSD_KERNEL_SCAN_F32 && a->kernel != SSD_KERNEL_TCGEN05)
+    return SSD_ERR_UNSUPPORTED;
+  if (a->nsegments < 0) return SSD_ERR_BAD_SHAPE;
+  if ((int64_t)a->batch * a->nheads > 0x7fffffffLL) return SSD_ERR_TOO_LARGE;
+  return SSD_OK;
+}
+
+int validate_pointers(const SsdArgs* a) {
+  if (!a->X || !a->A || !a->B) return SSD_ERR_NULL_POINTER;
+  const bool state_only = (a->flags & SSD_FLAG_STATE_ONLY) != 0;
+  if (!state_only && (!a->Y || !a->C)) return SSD_ERR_NULL_POINTER;
+  if (state_only && !a->final_state) return SSD_ERR_NULL_POINTER;
+  return SSD_OK;
+}
+
+int resolve_kernel(const SsdArgs* a) {
+  if (a->kernel == SSD_KERNEL_SCAN_F32) return SSD_KERNEL_SCAN_F32;
+  if (a->kernel == SSD_KERNEL_TCGEN05) return SSD_KERNEL_TCGEN05;
+  return ssd::tc_supports(*a) ? SSD_KERNEL_TCGEN05 : SSD_KERNEL_SCAN_F32;
+}
+
+int tile_tokens(int kernel) { return kernel == SSD_KERNEL_TCGEN05 ? 128 : ssd::scan_f32_tile_tokens(); }
+
+// Number of independently scanned segments per sequence and their length.
+void resolve_segments(const SsdArgs* a, int kernel, int* nseg, int* seg_len) {
+  const int tile = tile_tokens(kernel);
+  int want = a->nsegments;
+  if (want <= 0) {
+    if (kernel == SSD_KERNEL_TCGEN05) {
+      want = ssd::tc_default_segments(*a);
+    } else {
+      const int64_t units = (int64_t)a->batch * a->nheads;
+      // Two passes cost about 1.5x the work of one, so split only when the
+      // unsplit grid would leave most of the SMs idle.
+      want = units >= (3 * kSmCount) / 2 ? 1 : (int)((4 * kSmCount + units - 1) / units);
+      const int max_by_len = std::max(1, a->seqlen / 256);
+      want = std::min(want, max_by_len);
+    }
+  }
+  want = std::max(1, std::min(want, 65535));
+  int len = (a->seqlen + want - 1) / want;
+  len = (len + tile - 1) / tile * tile;
+  *seg_len = len;
+  *nseg = (a->seqlen + len - 1) / len;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+bool strides_mult(const int64_t* s, int m) { return s[0] % m == 0 && s[1] % m == 0 && s[2] % m == 0; }
+
+void fill_params(const SsdArgs* a, ssd::ScanParams* p) {
+  std::memset(p, 0, sizeof(*p));
+  p->X = a->X; p->A = a->A; p->B = a->B; p->C = a->C; p->dt = a->dt; p->Y = a->Y;
+  p->status = a->status;
+  p->batch = a->batch; p->seqlen = a->seqlen; p->nheads = a->nheads; p->p = a->headdim; p->n = a->dstate;
+  p->ngroups = a->ngroups;
+  for (int i = 0; i < 3; ++i) {
+    p->xs[i] = a->x_stride[i]; p->as[i] = a->a_stride[i]; p->bs[i] = a->b_stride[i];
+    p->cs[i] = a->c_stride[i]; p->dts[i] = a->dt_stride[i]; p->ys[i] = a->y_stride[i];
+  }
+  const int per16 = 16 / elem_size(a->dtype);
+  bool v = aligned16(a->X) && aligned16(a->B) && strides_mult(a->x_stride, per16) &&
+           strides_mult(a->b_stride, per16) && a->headdim % 8 == 0 && a->dstate % 8 == 0;
+  if (a->C) v = v && aligned16(a->C) && strides_mult(a->c_stride, per16);
+  if (a->Y) v = v && aligned16(a->Y) && strides_mult(a->y_stride, per16);
+  p->vec_ok = v ? 1 : 0;
+}
+
+int launch_kernel(int kernel, const SsdArgs* a, const ssd::ScanParams& prm, cudaStream_t stream) {
+  if (kernel == SSD_KERNEL_TCGEN05) return ssd::launch_tc(*a, prm, stream);
+  return ssd::launch_scan_f32(prm, a->dtype, stream);
+}
+
+}  // namespace
+
+extern "C" {
+
+int ssd_b200_abi_version(void) { return kAbiVersion; }
+
+const char* ssd_b200_strerror(int code) {
+  switch (code) {
+    case SSD_OK: return "ok";
+    case SSD_ERR_NULL_POINTER: return "a required pointer is NULL";
+    case SSD_ERR_BAD_SHAPE: return "invalid shape (sizes must be positive; n_heads must be divisible by n_groups)";
+    case SSD_ERR_BAD_CHUNK: return "seq_len must be a positive multiple of chunk";
+    case SSD_ERR_UNSUPPORTED: return "shape, dtype or kernel not supported by this build";
+    case SSD_ERR_WORKSPACE: return "workspace missing or too small";
+    case SSD_ERR_CUDA: return "a CUDA runtime call failed";
+    case SSD_ERR_MISALIGNED: return "pointer or stride not aligned for the selected kernel";
+    case SSD_ERR_TOO_LARGE: return "size beyond a fixed limit";
+    default: return "unknown error code";
+  }
+}
+
+const char* ssd_b200_kernel_name(const SsdArgs* args) {
+  if (validate(args) != SSD_OK) return "invalid";
+  return resolve_kernel(args) == SSD_KERNEL_TCGEN05 ? "tcgen05" : "scan_f32";
+}
+
+size_t ssd_b200_workspace_bytes(const SsdArgs* args) {
+  if (validate(args) != SSD_OK) return 0;
+  const int kernel = resolve_kernel(args);
+  int nseg, seg_len;
+  resolve_segments(args, kernel, &nseg, &seg_len);
+  if (nseg <= 1) return 0;
+  const size_t units = (size_t)args->batch * args->nheads;
+  const size_t np = (size_t)args->dstate * args->headdim;
+  return align_up(units * nseg * np * sizeof(float), 256) + align_up(units * nseg * sizeof(float), 256);
+}
+
+int ssd_b200_forward(const SsdArgs* args, void* stream_v) {
+  int rc = validate(args);
+  if (rc != SSD_OK) return rc;
+  rc = validate_pointers(args);
+  if (rc != SSD_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const int kernel = resolve_kernel(args);
+  if (kernel == SSD_KERNEL_TCGEN05 && !ssd::tc_supports(*args)) return SSD_ERR_UNSUPPORTED;
+  if (kernel == SSD_KERNEL_SCAN_F32 && !ssd::scan_f32_supports(args->headdim, args->dstate))
+    return SSD_ERR_UNSUPPORTED;
+
+  int nseg, seg_len;
+  resolve_segments(args, kernel, &nseg, &seg_len);
+  const bool state_only = (args->flags & SSD_FLAG_STATE_ONLY) != 0;
+  const int64_t units = (int64_t)args->batch * args->nheads;
+  const int64_t np = (int64_t)args->dstate * args->headdim;
+
+  ssd::ScanParams prm;
+  fill_params(args, &prm);
+  prm.seg_len = seg_len;
+  prm.nseg = nseg;
+
+  if (nseg <= 1) {
+    prm.compute_y = state_only ? 0 : 1;
+    prm.init = args->initial_state;
+    prm.init_unit_stride = np;
+    prm.fin = args->final_state;
+    prm.fin_unit_stride = np;
+    prm.fin_ld = args->final_logdecay;
+    prm.finld_unit_stride = 1;
+    return launch_kernel(kernel, args, prm, stream);
+  }
+
+  const size_t need = ssd_b200_workspace_bytes(args);
+  if (!args->workspace || args->workspace_bytes < need) return SSD_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(args->workspace) & 255) return SSD_ERR_MISALIGNED;
+  float* seg_states = static_cast<float*>(args->workspace);
+  float* seg_ld = reinterpret_cast<float*>(static_cast<char*>(args->workspace) +
+                                            align_up((size_t)units * nseg * np * sizeof(float), 256));
+
+  // pass 1: every segment from a zero state, state and log-decay sum only
+  ssd::ScanParams p1 = prm;
+  p1.compute_y = 0;
+  p1.Y = nullptr;
+  p1.init = nullptr;
+  p1.fin = seg_states;
+  p1.fin_unit_stride = (int64_t)nseg * np;
+  p1.fin_seg_stride = np;
+  p1.fin_ld = seg_ld;
+  p1.finld_unit_stride = nseg;
+  p1.finld_seg_stride = 1;
+  rc = launch_kernel(kernel, args, p1, stream);
+  if (rc != SSD_OK) return rc;
+
+  // fold: state entering each segment (in place), final state, total log-decay
+  rc = ssd::launch_fold(seg_states, (int64_t)nseg * np, np, seg_ld, nseg, 1, args->initial_state, nullptr,
+                        args->final_state, args->final_logdecay, nseg, 1, units, np, stream);
+  if (rc != SSD_OK || state_only) return rc;
+
+  // pass 2: every segment again, seeded with its incoming state, writing Y
+  ssd::ScanParams p2 = prm;
+  p2.compute_y = 1;
+  p2.init = seg_states;
+  p2.init_unit_stride = (int64_t)nseg * np;
+  p2.init_seg_stride = np;
+  p2.fin = nullptr;
+  p2.fin_ld = nullptr;
+  return launch_kernel(kernel, args, p2, stream);
+}
+
+int ssd_b200_fold_states(const float* states, int64_t states_shard_stride, const float* logdecay,
+                         int64_t logdecay_shard_stride, const float* initial, float* out, int32_t nshards,
+                         int32_t rank, int64_t units, int64_t np, void* stream) {
+  if (!states || !logdecay || !out) return SSD_ERR_NULL_POINTER;
+  if (nshards <= 0 || rank < 0 || rank > nshards || units <= 0 || np <= 0) return SSD_ERR_BAD_SHAPE;
+  return ssd::launch_fold(const_cast<float*>(states), np, states_shard_stride, logdecay, 1, logdecay_shard_stride,
+                          initial, out, nullptr, nullptr, rank, 0, units, np, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

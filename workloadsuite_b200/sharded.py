@@ -1,0 +1,119 @@
+"""Multi-GPU partitioning of the SSD forward: one process per GPU.
+
+Two partitionings, neither present in the single-device reference:
+
+* **heads** -- every (batch, head) pair is an independent scan, so heads are split
+  across ranks with no data-path collective; B/C of a group travel with its heads.
+* **sequence** -- the recurrence is linear in the state, so each rank scans its
+  token shard from a zero state, the ranks exchange only that final state and the
+  shard's summed log-decay (one NCCL all-gather over NVLink; 1 MiB per rank at
+  h=32, n=128, p=64), and each rank re-scans its shard seeded with the folded
+  state of its predecessors.
+
+The compute callables are injectable so that the exchange algebra runs on CPU
+``gloo`` ranks in the tests; the defaults are the CUDA kernels and never fall back.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def head_shard_bounds(n_heads: int, n_groups: int, rank: int, world: int) -> Tuple[int, int, int, int]:
+    """(h0, h1, g0, g1): heads [h0,h1) and B/C groups [g0,g1) owned by ``rank``.
+
+    Heads are split evenly; a rank's heads are whole groups, or lie inside one group.
+    """
+    if n_heads % n_groups != 0:
+        raise ValueError("n_heads must be divisible by n_groups")
+    if n_heads % world != 0:
+        raise ValueError(f"n_heads={n_heads} is not divisible by world size {world}")
+    hl = n_heads // world
+    hpg = n_heads // n_groups
+    if not (hl % hpg == 0 or hpg % hl == 0):
+        raise ValueError(f"{hl} heads per rank do not align with groups of {hpg} heads")
+    h0, h1 = rank * hl, (rank + 1) * hl
+    g0 = h0 // hpg
+    g1 = max(g0 + 1, h1 // hpg)
+    return h0, h1, g0, g1
+
+
+def shard_heads(X, A, B, C, rank: int, world: int, dt=None, initial_states=None):
+    """Slice full tensors to the head shard of ``rank`` (views, no copies)."""
+    h, g = X.shape[2], B.shape[2]
+    h0, h1, g0, g1 = head_shard_bounds(h, g, rank, world)
+    out = dict(X=X[:, :, h0:h1], A=A[:, :, h0:h1], B=B[:, :, g0:g1], C=C[:, :, g0:g1])
+    if dt is not None:
+        out["dt"] = dt[:, :, h0:h1]
+    if initial_states is not None:
+        out["initial_states"] = initial_states[:, h0:h1]
+    return out
+
+
+def _cuda_scan(X, A, B, C, chunk, dt=None, initial_states=None, state_only=False, **kw):
+    from .ssd import ssd_forward
+
+    if state_only:
+        return ssd_forward(X, A, B, C, chunk, dt=dt, initial_states=initial_states, state_only=True,
+                           return_logdecay=True, **kw)
+    return ssd_forward(X, A, B, C, chunk, dt=dt, initial_states=initial_states, **kw)
+
+
+def _cuda_fold(states, logdecays, rank, initial=None):
+    from .ssd import fold_states
+
+    return fold_states(states, logdecays, rank, initial)
+
+
+class SequenceShardedSSD:
+    """SSD forward over a sequence split evenly across the ranks of ``group``.
+
+    Rank r holds tokens ``[r*s/R, (r+1)*s/R)`` of every tensor.  ``forward`` returns
+    the local Y shard.  Buffers for the exchange are allocated once per shape.
+    """
+
+    def __init__(self, group: Optional[dist.ProcessGroup] = None, scan_fn: Callable = _cuda_scan,
+                 fold_fn: Callable = _cuda_fold):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.scan_fn = scan_fn
+        self.fold_fn = fold_fn
+        self._send = None
+        self._recv = None
+
+    def _buffers(self, numel: int, device):
+        if self._send is None or self._send.numel() != numel or self._send.device != device:
+            self._send = torch.empty(numel, dtype=torch.float32, device=device)
+            self._recv = torch.empty(self.world * numel, dtype=torch.float32, device=device)
+        return self._send, self._recv
+
+    def forward(self, X, A, B, C, chunk, dt=None, initial_states=None, **kw):
+        b, s_loc, h, p = X.shape
+        n = B.shape[3]
+        # phase 1: local scan from zero, final state and summed log-decay only
+        F, D = self.scan_fn(X, A, B, C, chunk, dt=dt, initial_states=None, state_only=True, **kw)
+        ns, nd = F.numel(), D.numel()
+        send, recv = self._buffers(ns + nd, F.device)
+        send[:ns].copy_(F.reshape(-1))
+        send[ns:].copy_(D.reshape(-1))
+        # phase 2: the only collective -- every rank's (state, log-decay) to every rank
+        dist.all_gather_into_tensor(recv, send, group=self.group)
+        recv = recv.view(self.world, ns + nd)
+        states = recv[:, :ns].unflatten(1, (b, h, n, p))
+        lds = recv[:, ns:].unflatten(1, (b, h))
+        # phase 3: fold the predecessors, then the real scan seeded with the result
+        # (initial_states, the state before token 0 of the whole sequence, is replicated on all ranks)
+        h_in = initial_states if self.rank == 0 else self.fold_fn(states, lds, self.rank, initial_states)
+        return self.scan_fn(X, A, B, C, chunk, dt=dt, initial_states=h_in, state_only=False, **kw)
+
+
+def sequence_sharded_forward(X, A, B, C, chunk, group=None, dt=None, initial_states=None, **kw):
+    """Functional form of :class:`SequenceShardedSSD` (allocates its buffers per call).
+
+    ``initial_states`` (the state before token 0 of the whole sequence) must be
+    passed identically on every rank, or be None.
+    """
+    return SequenceShardedSSD(group).forward(X, A, B, C, chunk, dt=dt, initial_states=initial_states, **kw)

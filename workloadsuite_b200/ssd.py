@@ -1,0 +1,254 @@
+"""Functional SSD forward on B200: ``ssd_forward`` and its host-buffer variant.
+
+Replaces ``SSDLayer._ssd_core`` of the reference (``workloads/mamba/model_ref.py:123-162``)
+with hand-written sm_100a kernels reached through the C ABI of ``include/ssd_b200.h``.
+PyTorch supplies device memory and the current stream only.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.float32: _lib.DTYPE_F32, torch.float16: _lib.DTYPE_F16, torch.bfloat16: _lib.DTYPE_BF16}
+_KERNELS = {None: _lib.KERNEL_AUTO, "auto": _lib.KERNEL_AUTO, "scan_f32": _lib.KERNEL_SCAN_F32,
+            "tcgen05": _lib.KERNEL_TCGEN05}
+
+_workspaces: dict = {}
+
+
+class SsdError(RuntimeError):
+    """An SSD_ERR_* code from the native library that has no closer Python exception."""
+
+
+def _raise(code: int):
+    msg = f"{_lib.ERRORS.get(code, code)}: {_lib.strerror(code)}"
+    if code in (-2, -3):
+        # the reference raises ValueError for bad head/group counts (model_ref.py:37-38) and an
+        # einops error (a ValueError-like shape error) for seq_len % block_len != 0 (model_ref.py:106)
+        raise ValueError(msg)
+    if code == -4:
+        raise NotImplementedError(msg)
+    raise SsdError(msg)
+
+
+def _strides3(t: torch.Tensor, name: str):
+    if t.stride(-1) != 1 and t.shape[-1] != 1:
+        raise ValueError(f"{name}: innermost axis must be contiguous")
+    return (C.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+
+
+def _check(X, A, B, Cm, dt, initial_states):
+    if X.dim() != 4 or A.dim() != 3 or B.dim() != 4 or Cm.dim() != 4:
+        raise ValueError("expected X[b,s,h,p], A[b,s,h], B[b,s,g,n], C[b,s,g,n]")
+    b, s, h, p = X.shape
+    g, n = B.shape[2], B.shape[3]
+    if A.shape != (b, s, h) or B.shape[:2] != (b, s) or Cm.shape != B.shape:
+        raise ValueError("inconsistent shapes")
+    if X.dtype not in _DTYPES or B.dtype != X.dtype or Cm.dtype != X.dtype:
+        raise TypeError("X, B, C must share one dtype of float32/float16/bfloat16")
+    if A.dtype != torch.float32:
+        raise TypeError("A (per-token log-decay) must be float32")
+    if dt is not None and (dt.shape != (b, s, h) or dt.dtype != X.dtype):
+        raise ValueError("dt must be [b,s,h] in the dtype of X")
+    if initial_states is not None and (initial_states.shape != (b, h, n, p) or initial_states.dtype != torch.float32):
+        raise ValueError("initial_states must be float32 [b,h,n,p]")
+    return b, s, h, p, g, n
+
+
+def _fill(args, X, A, B, Cm, dt, initial_states, Y, final_state, final_ld, chunk, kernel, nsegments, state_only):
+    b, s, h, p = X.shape
+    args.X, args.A, args.B, args.C = X.data_ptr(), A.data_ptr(), B.data_ptr(), Cm.data_ptr()
+    args.dt = dt.data_ptr() if dt is not None else None
+    args.initial_state = initial_states.data_ptr() if initial_states is not None else None
+    args.Y = Y.data_ptr() if Y is not None else None
+    args.final_state = final_state.data_ptr() if final_state is not None else None
+    args.final_logdecay = final_ld.data_ptr() if final_ld is not None else None
+    args.batch, args.seqlen, args.nheads, args.headdim = b, s, h, p
+    args.dstate, args.ngroups = B.shape[3], B.shape[2]
+    args.chunk = chunk
+    args.dtype = _DTYPES[X.dtype]
+    if kernel not in _KERNELS:
+        raise ValueError(f"kernel must be one of {sorted(k for k in _KERNELS if k)}")
+    args.kernel = _KERNELS[kernel]
+    args.flags = _lib.FLAG_STATE_ONLY if state_only else 0
+    args.nsegments = int(nsegments or 0)
+    args.x_stride = _strides3(X, "X")
+    args.a_stride = (C.c_int64 * 3)(*A.stride())
+    args.b_stride = _strides3(B, "B")
+    args.c_stride = _strides3(Cm, "C")
+    if dt is not None:
+        args.dt_stride = (C.c_int64 * 3)(*dt.stride())
+    if Y is not None:
+        args.y_stride = _strides3(Y, "Y")
+
+
+def _workspace(device, nbytes: int) -> Optional[torch.Tensor]:
+    if nbytes == 0:
+        return None
+    key = (device.type, device.index)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def ssd_forward(
+    X: torch.Tensor,
+    A: torch.Tensor,
+    B: torch.Tensor,
+    C_: torch.Tensor,
+    chunk: int,
+    dt: Optional[torch.Tensor] = None,
+    initial_states: Optional[torch.Tensor] = None,
+    return_final_state: bool = False,
+    return_logdecay: bool = False,
+    state_only: bool = False,
+    kernel: Optional[str] = None,
+    nsegments: Optional[int] = None,
+    out: Optional[torch.Tensor] = None,
+):
+    """Mamba-2 SSD forward ``Y = SSD(X, A, B, C)`` on the current CUDA stream.
+
+    X [b,s,h,p]; A [b,s,h] float32 per-token log-decay (the reference's ``A_dt``,
+    ``model_ref.py:103``); B, C [b,s,g,n] *ungrouped* (head j reads group
+    ``j // (h//g)``, ``model_ref.py:97-99``); dt [b,s,h] or None for ``X`` already
+    scaled (``model_ref.py:144``); initial_states float32 [b,h,n,p] (the layout of
+    the carry at ``model_ref.py:153``) or None for zeros.  ``chunk`` is the
+    reference's ``block_len``: it must divide ``s`` (as at ``model_ref.py:106``);
+    the result does not otherwise depend on it.  Views with a contiguous innermost
+    axis are accepted as they are.  No host synchronisation.
+
+    Returns Y [b,s,h,p] in X's dtype, plus the float32 final state [b,h,n,p] and/or
+    the summed log-decay [b,h] when asked.  With ``state_only`` no Y is produced.
+    """
+    if not X.is_cuda:
+        raise RuntimeError("ssd_forward needs CUDA tensors (there is no CPU path); see ssd_forward_host")
+    b, s, h, p, g, n = _check(X, A, B, C_, dt, initial_states)
+    if h % g != 0:
+        raise ValueError("n_heads must be divisible by n_groups")
+    if initial_states is not None:
+        initial_states = initial_states.contiguous()
+    lib = _lib.load()
+    dev = X.device
+    want_final = return_final_state or state_only
+    Y = None
+    if not state_only:
+        Y = out if out is not None else torch.empty((b, s, h, p), dtype=X.dtype, device=dev)
+    final_state = torch.empty((b, h, n, p), dtype=torch.float32, device=dev) if want_final else None
+    final_ld = torch.empty((b, h), dtype=torch.float32, device=dev) if return_logdecay else None
+    args = _lib.SsdArgs()
+    _fill(args, X, A, B, C_, dt, initial_states, Y, final_state, final_ld, chunk, kernel, nsegments, state_only)
+    with torch.cuda.device(dev):
+        need = lib.ssd_b200_workspace_bytes(C.byref(args))
+        ws = _workspace(dev, need)
+        if ws is not None:
+            args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
+        rc = lib.ssd_b200_forward(C.byref(args), C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    if rc != _lib.SSD_OK:
+        _raise(rc)
+    outs = [] if state_only else [Y]
+    if want_final:
+        outs.append(final_state)
+    if return_logdecay:
+        outs.append(final_ld)
+    return outs[0] if len(outs) == 1 else tuple(outs)
+
+
+def kernel_name(X, A, B, C_, chunk, kernel=None) -> str:
+    """Which kernel family ``ssd_forward`` would run for these tensors."""
+    _check(X, A, B, C_, None, None)
+    args = _lib.SsdArgs()
+    _fill(args, X, A, B, C_, None, None, None, None, None, chunk, kernel, 0, False)
+    return _lib.load().ssd_b200_kernel_name(C.byref(args)).decode()
+
+
+def fold_states(states: torch.Tensor, logdecays: torch.Tensor, rank: int,
+                initial: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """State entering shard ``rank`` of a sequence-sharded scan.
+
+    states float32 [R,b,h,n,p] (each shard's final state when scanned from zero),
+    logdecays float32 [R,b,h]; both may be strided along R (slices of one
+    all-gather buffer).  ``H_in(r+1) = exp(D_r) H_in(r) + F_r``.
+    """
+    R, b, h, n, p = states.shape
+    if not states[0].is_contiguous() or not logdecays[0].is_contiguous():
+        states, logdecays = states.contiguous(), logdecays.contiguous()
+    if states.dtype != torch.float32 or logdecays.dtype != torch.float32:
+        raise TypeError("states and logdecays must be float32")
+    if initial is not None:
+        initial = initial.contiguous()
+    out = torch.empty((b, h, n, p), dtype=torch.float32, device=states.device)
+    lib = _lib.load()
+    with torch.cuda.device(states.device):
+        rc = lib.ssd_b200_fold_states(states.data_ptr(), states.stride(0) if R > 1 else b * h * n * p,
+                                      logdecays.data_ptr(), logdecays.stride(0) if R > 1 else b * h,
+                                      initial.data_ptr() if initial is not None else None, out.data_ptr(), R, rank,
+                                      b * h, n * p, C.c_void_p(torch.cuda.current_stream(states.device).cuda_stream))
+    if rc != _lib.SSD_OK:
+        _raise(rc)
+    return out
+
+
+class HostRunner:
+    """Reusable host-buffer forward: owns the device scratch for one problem shape.
+
+    ``run`` takes CPU tensors (pinned memory gives full PCIe rate), copies them to
+    the GPU in slices, computes and copies Y back into ``out``; it returns after
+    the result is in host memory.
+    """
+
+    def __init__(self, b, s, h, p, n, g, chunk, dtype, device="cuda:0", kernel=None, has_dt=False):
+        self.shape = (b, s, h, p, n, g)
+        self.chunk, self.dtype, self.kernel = chunk, dtype, kernel
+        self.device = torch.device(device)
+        self.lib = _lib.load()
+        a = _lib.SsdArgs()
+        a.batch, a.seqlen, a.nheads, a.headdim, a.dstate, a.ngroups = b, s, h, p, n, g
+        a.chunk, a.dtype, a.kernel = chunk, _DTYPES[dtype], _KERNELS[kernel]
+        a.dt = 1 if has_dt else None  # only NULL-ness matters for sizing
+        with torch.cuda.device(self.device):
+            nbytes = self.lib.ssd_b200_host_scratch_bytes(C.byref(a))
+            if nbytes == 0:
+                raise ValueError("invalid problem shape")
+            self.scratch = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    def run(self, X, A, B, C_, out, dt=None, initial_states=None, final_state=None):
+        b, s, h, p, n, g = self.shape
+        for t in (X, A, B, C_, out):
+            if t.is_cuda or not t.is_contiguous():
+                raise ValueError("HostRunner.run takes contiguous CPU tensors")
+        a = _lib.SsdArgs()
+        a.batch, a.seqlen, a.nheads, a.headdim, a.dstate, a.ngroups = b, s, h, p, n, g
+        a.chunk, a.dtype, a.kernel = self.chunk, _DTYPES[self.dtype], _KERNELS[self.kernel]
+        a.X, a.A, a.B, a.C, a.Y = X.data_ptr(), A.data_ptr(), B.data_ptr(), C_.data_ptr(), out.data_ptr()
+        a.dt = dt.data_ptr() if dt is not None else None
+        a.initial_state = initial_states.data_ptr() if initial_states is not None else None
+        a.final_state = final_state.data_ptr() if final_state is not None else None
+        with torch.cuda.device(self.device):
+            rc = self.lib.ssd_b200_forward_host(C.byref(a), self.scratch.data_ptr(), self.scratch.numel())
+        if rc != _lib.SSD_OK:
+            _raise(rc)
+        self.h2d_bytes = sum(t.numel() * t.element_size() for t in (X, A, B, C_, dt, initial_states) if t is not None)
+        self.d2h_bytes = sum(t.numel() * t.element_size() for t in (out, final_state) if t is not None)
+        return out
+
+
+def ssd_forward_host(X, A, B, C_, chunk, dt=None, initial_states=None, kernel=None, device="cuda:0"):
+    """One-shot host-buffer forward: CPU tensors in, CPU tensor out (computed on the GPU)."""
+    b, s, h, p, g, n = _check(X, A, B, C_, dt, initial_states)
+    if h % g != 0:
+        raise ValueError("n_heads must be divisible by n_groups")
+    if s % chunk != 0:
+        raise ValueError("seq_len must be a multiple of chunk")
+    r = HostRunner(b, s, h, p, n, g, chunk, X.dtype, device=device, kernel=kernel, has_dt=dt is not None)
+    out = torch.empty_like(X).contiguous()
+    return r.run(X.contiguous(), A.contiguous(), B.contiguous(), C_.contiguous(), out,
+                 dt=None if dt is None else dt.contiguous(),
+                 initial_states=None if initial_states is None else initial_states.contiguous())
