@@ -1,0 +1,327 @@
+"""Parity of the CUDA SSD forward (called through the C ABI) with the CPU oracle.
+
+Tolerances (worst per-(batch, head) max-abs error over max-abs reference, and global
+relative Frobenius error): 1e-4 for float32, 2e-2 for bfloat16/float16 -- the figures
+the task states per dtype.  The oracle is the float64 token recurrence unless a golden
+output of the reference itself is available."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import ssd_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float32: 1e-4, torch.float16: 2e-2, torch.bfloat16: 2e-2}
+DEV = "cuda:0"
+
+
+def _ssd():
+    import workloadsuite_b200 as W
+
+    return W
+
+
+def _kernels_for(dtype, p, n):
+    ks = ["scan_f32"]
+    if dtype in (torch.float16, torch.bfloat16) and p == 64 and n in (64, 128):
+        ks.append("tcgen05")
+    return ks
+
+
+def _tc_available():
+    W = _ssd()
+    X = torch.zeros(1, 128, 1, 64, dtype=torch.bfloat16, device=DEV)
+    A = torch.zeros(1, 128, 1, device=DEV)
+    B = torch.zeros(1, 128, 1, 128, dtype=torch.bfloat16, device=DEV)
+    return W.kernel_name(X, A, B, B, 128) == "tcgen05"
+
+
+def _to_dev(inp):
+    return {k: v.to(DEV) for k, v in inp.items()}
+
+
+def _run_and_check(inp, chunk, kernel=None, tol=None, dt=None, **kw):
+    W = _ssd()
+    d = _to_dev(inp)
+    init = d.get("initial_states")
+    dtd = dt.to(DEV) if dt is not None else None
+    out = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], chunk, dt=dtd, initial_states=init, return_final_state=True,
+                        kernel=kernel, **kw)
+    Y, H = out
+    torch.cuda.synchronize()
+    Yr, Hr = O.ssd_recurrence(inp["X"], inp["A"], inp["B"], inp["C"], dt=dt, initial_states=inp.get("initial_states"),
+                              return_final_state=True)
+    per_bh, fro = O.error_metrics(Y.cpu(), Yr)
+    tol = tol or TOL[inp["X"].dtype]
+    assert per_bh < tol and fro < tol, (kernel, per_bh, fro)
+    herr = ((H.cpu().double() - Hr).abs().amax(dim=(2, 3)) / Hr.abs().amax(dim=(2, 3)).clamp_min(1e-30)).max().item()
+    assert herr < tol, ("final state", kernel, herr)
+    return Y, H
+
+
+# ---------------------------------------------------------------- golden fixtures (reference outputs)
+
+@pytest.mark.parametrize("name", ["core_n16_q64", "core_n128_q64_slow", "core_n64_grouped_q32", "core_n128_q128_dt"])
+def test_matches_reference_golden_fp16(golden_dir, name):
+    W = _ssd()
+    z = np.load(golden_dir / f"{name}.npz")
+    d = {k: torch.from_numpy(z[k]).to(DEV) for k in z.files if k != "chunk"}
+    chunk = int(z["chunk"])
+    n = d["B"].shape[-1]
+    for kernel in _kernels_for(torch.float16, 64, n):
+        if kernel == "tcgen05" and not _tc_available():
+            continue
+        Y = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], chunk, dt=d.get("dt"), kernel=kernel)
+        per_bh, fro = O.error_metrics(Y.cpu(), d["Y"].cpu())
+        assert per_bh < 2e-2 and fro < 2e-2, (name, kernel, per_bh, fro)
+
+
+# ---------------------------------------------------------------- the benchmark configurations
+
+def test_config0_fp32_full_size():
+    cfg = dict(O.CONFIGS["cfg0"])
+    inp = O.make_inputs(seed=0, **cfg)
+    _run_and_check(inp, cfg["chunk"])
+
+
+SHRUNK = {
+    # same head/state geometry and distributions as the named config, fewer tokens/heads
+    "cfg1": dict(b=2, s=512, h=3, p=64, n=128, g=1, chunk=256, dtype="bf16", decay="mamba"),
+    "cfg2": dict(b=1, s=1024, h=4, p=64, n=128, g=1, chunk=256, dtype="bf16", decay="mamba"),
+    "cfg3": dict(b=1, s=2048, h=2, p=64, n=128, g=1, chunk=256, dtype="bf16", decay="mamba"),
+    "cfg4": dict(b=3, s=512, h=12, p=64, n=64, g=2, chunk=128, dtype="bf16", init=True, decay="mamba"),
+}
+
+
+@pytest.mark.parametrize("name", sorted(SHRUNK))
+@pytest.mark.parametrize("decay_scale", [1.0, 0.02])
+def test_shrunken_configs_bf16(name, decay_scale):
+    cfg = dict(SHRUNK[name])
+    inp = O.make_inputs(seed=1, decay_scale=decay_scale, **cfg)
+    for kernel in _kernels_for(torch.bfloat16, cfg["p"], cfg["n"]):
+        if kernel == "tcgen05" and not _tc_available():
+            continue
+        _run_and_check(inp, cfg["chunk"], kernel=kernel)
+
+
+# ---------------------------------------------------------------- edge cases
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_single_chunk_and_many_chunks(dtype):
+    for s, chunk in [(64, 64), (128, 128), (1024, 32)]:
+        inp = O.make_inputs(b=1, s=s, h=2, p=64, n=64, g=2, dtype=dtype, seed=2, decay_scale=0.1)
+        for kernel in _kernels_for(dtype, 64, 64):
+            if kernel == "tcgen05" and (not _tc_available() or s % 128):
+                continue
+            _run_and_check(inp, chunk, kernel=kernel)
+
+
+@pytest.mark.parametrize("g", [1, 2, 8])
+def test_group_counts(g):
+    inp = O.make_inputs(b=2, s=256, h=8, p=64, n=64, g=g, dtype=torch.bfloat16, seed=3, decay_scale=0.05)
+    for kernel in _kernels_for(torch.bfloat16, 64, 64):
+        if kernel == "tcgen05" and not _tc_available():
+            continue
+        _run_and_check(inp, 128, kernel=kernel)
+
+
+def test_initial_state_axis_order_with_p_not_equal_n():
+    # state layout is [b,h,n,p] (the carry of model_ref.py:153); p=32, n=64 tells the axes apart
+    inp = O.make_inputs(b=2, s=128, h=4, p=32, n=64, g=1, dtype=torch.float32, init=True, seed=4, decay_scale=0.05)
+    _run_and_check(inp, 64)
+    inp = O.make_inputs(b=1, s=128, h=2, p=128, n=32, g=2, dtype=torch.float32, init=True, seed=4, decay_scale=0.05)
+    _run_and_check(inp, 64)
+
+
+def test_fast_decay_underflows_cleanly():
+    inp = O.make_inputs(b=1, s=256, h=2, p=64, n=128, g=1, dtype=torch.bfloat16, seed=5, decay_scale=40.0)
+    for kernel in _kernels_for(torch.bfloat16, 64, 128):
+        if kernel == "tcgen05" and not _tc_available():
+            continue
+        Y, H = _run_and_check(inp, 128, kernel=kernel)
+        assert torch.isfinite(Y).all() and torch.isfinite(H).all()
+
+
+def test_dt_scaling():
+    inp = O.make_inputs(b=1, s=256, h=2, p=64, n=64, g=1, dtype=torch.float16, seed=6, decay_scale=0.1)
+    dt = (torch.rand(1, 256, 2) + 0.5).half()
+    for kernel in _kernels_for(torch.float16, 64, 64):
+        if kernel == "tcgen05" and not _tc_available():
+            continue
+        _run_and_check(inp, 64, kernel=kernel, dt=dt)
+
+
+def test_strided_views_are_accepted():
+    W = _ssd()
+    inp = O.make_inputs(b=2, s=256, h=4, p=64, n=64, g=2, dtype=torch.bfloat16, seed=7, decay_scale=0.1)
+    d = _to_dev(inp)
+    # X, B, C as slices of one wide projection output, the way the block produces them (model_ref.py:76)
+    wide = torch.zeros(2, 256, 4 * 64 + 2 * 2 * 64 + 8, dtype=torch.bfloat16, device=DEV)
+    wide[..., : 256] = d["X"].flatten(2)
+    wide[..., 256: 384] = d["B"].flatten(2)
+    wide[..., 384: 512] = d["C"].flatten(2)
+    Xv = wide[..., :256].unflatten(-1, (4, 64))
+    Bv = wide[..., 256:384].unflatten(-1, (2, 64))
+    Cv = wide[..., 384:512].unflatten(-1, (2, 64))
+    assert not Xv.is_contiguous()
+    for kernel in _kernels_for(torch.bfloat16, 64, 64):
+        if kernel == "tcgen05" and not _tc_available():
+            continue
+        Y1 = W.ssd_forward(Xv, d["A"], Bv, Cv, 128, kernel=kernel)
+        Y2 = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], 128, kernel=kernel)
+        assert torch.equal(Y1, Y2)
+
+
+def test_ragged_and_invalid_arguments_raise():
+    W = _ssd()
+    inp = _to_dev(O.make_inputs(b=1, s=192, h=4, p=64, n=64, g=2, dtype=torch.float32, seed=8))
+    with pytest.raises(ValueError):
+        W.ssd_forward(inp["X"], inp["A"], inp["B"], inp["C"], 128)          # 192 % 128 (model_ref.py:106)
+    bad = _to_dev(O.make_inputs(b=1, s=128, h=4, p=64, n=64, g=3, dtype=torch.float32, seed=8))
+    with pytest.raises(ValueError):
+        W.ssd_forward(bad["X"], bad["A"], bad["B"], bad["C"], 64)           # 4 % 3 (model_ref.py:37-38)
+    odd = _to_dev(O.make_inputs(b=1, s=64, h=2, p=48, n=16, g=1, dtype=torch.float32, seed=8))
+    with pytest.raises(NotImplementedError):
+        W.ssd_forward(odd["X"], odd["A"], odd["B"], odd["C"], 64)           # head dim outside the kernels
+
+
+# ---------------------------------------------------------------- segmentation (scratch-memory path)
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_segmented_scan_equals_unsegmented(dtype):
+    inp = O.make_inputs(b=1, s=1024, h=2, p=64, n=64, g=1, dtype=dtype, init=True, seed=9, decay_scale=0.02)
+    for kernel in _kernels_for(dtype, 64, 64):
+        if kernel == "tcgen05" and not _tc_available():
+            continue
+        Y1, H1 = _run_and_check(inp, 128, kernel=kernel, nsegments=1)
+        Y4, H4 = _run_and_check(inp, 128, kernel=kernel, nsegments=4)
+        assert O.error_metrics(Y4.cpu(), Y1.cpu())[0] < TOL[dtype]
+        Y3, _ = _run_and_check(inp, 128, kernel=kernel, nsegments=3)   # last segment shorter
+        assert O.error_metrics(Y3.cpu(), Y1.cpu())[0] < TOL[dtype]
+
+
+def test_state_only_and_logdecay_outputs():
+    W = _ssd()
+    inp = O.make_inputs(b=2, s=512, h=3, p=64, n=64, g=1, dtype=torch.bfloat16, seed=10, decay_scale=0.05)
+    d = _to_dev(inp)
+    for nseg in (1, 4):
+        H, D = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], 128, state_only=True, return_logdecay=True,
+                             kernel="scan_f32", nsegments=nseg)
+        _, Hr = O.ssd_recurrence(inp["X"], inp["A"], inp["B"], inp["C"], return_final_state=True)
+        assert ((H.cpu().double() - Hr).abs().max() / Hr.abs().max()) < 1e-4
+        assert torch.allclose(D.cpu().double(), O.total_logdecay(inp["A"]), rtol=1e-5, atol=1e-6)
+
+
+def test_fold_states_matches_oracle():
+    W = _ssd()
+    gen = torch.Generator().manual_seed(11)
+    states = torch.randn(4, 2, 3, 16, 8, generator=gen)
+    lds = -torch.rand(4, 2, 3, generator=gen)
+    init = torch.randn(2, 3, 16, 8, generator=gen)
+    for r in range(5):
+        got = W.fold_states(states.to(DEV), lds.to(DEV), r, init.to(DEV)).cpu()
+        want = O.fold_incoming_state(states, lds, r, init)
+        assert torch.allclose(got.double(), want, rtol=1e-5, atol=1e-6)
+
+
+def test_run_to_run_determinism():
+    W = _ssd()
+    inp = _to_dev(O.make_inputs(b=2, s=512, h=4, p=64, n=128, g=1, dtype=torch.bfloat16, seed=12))
+    for kernel in _kernels_for(torch.bfloat16, 64, 128):
+        if kernel == "tcgen05" and not _tc_available():
+            continue
+        Y1 = W.ssd_forward(inp["X"], inp["A"], inp["B"], inp["C"], 256, kernel=kernel)
+        Y2 = W.ssd_forward(inp["X"], inp["A"], inp["B"], inp["C"], 256, kernel=kernel)
+        assert torch.equal(Y1, Y2)
+
+
+# ---------------------------------------------------------------- full-size configurations: properties
+
+def _full(name, seed=0):
+    cfg = dict(O.CONFIGS[name])
+    return cfg, O.make_inputs(seed=seed, **cfg)
+
+
+@pytest.mark.parametrize("name", ["cfg1", "cfg2"])
+def test_full_size_properties(name):
+    """At full size the oracle is too slow for every unit, so check (i) a sample of
+    (batch, head) units against it, (ii) exact homogeneity Y(2X) == 2 Y(X) (scaling by two
+    is exact in binary floating point) and (iii) splitting the sequence in two with the
+    carried state reproduces the one-pass result."""
+    W = _ssd()
+    cfg, inp = _full(name)
+    d = _to_dev(inp)
+    chunk = cfg["chunk"]
+    Y = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], chunk)
+    assert torch.isfinite(Y).all()
+    # (i) sampled units
+    for (bi, hi) in [(0, 0), (cfg["b"] - 1, cfg["h"] - 1), (cfg["b"] // 2, cfg["h"] // 3)]:
+        Yr = O.ssd_recurrence(inp["X"][bi:bi + 1, :, hi:hi + 1], inp["A"][bi:bi + 1, :, hi:hi + 1],
+                              inp["B"][bi:bi + 1], inp["C"][bi:bi + 1])
+        per_bh, fro = O.error_metrics(Y[bi:bi + 1, :, hi:hi + 1].cpu(), Yr)
+        assert per_bh < 2e-2 and fro < 2e-2, (bi, hi, per_bh, fro)
+    # (ii) homogeneity, bitwise
+    Y2 = W.ssd_forward(d["X"] * 2, d["A"], d["B"], d["C"], chunk)
+    assert torch.equal(Y2, Y * 2)
+    # (iii) split + carry
+    half = cfg["s"] // 2
+    Ya, Ha = W.ssd_forward(d["X"][:, :half], d["A"][:, :half], d["B"][:, :half], d["C"][:, :half], chunk,
+                           return_final_state=True)
+    Yb = W.ssd_forward(d["X"][:, half:], d["A"][:, half:], d["B"][:, half:], d["C"][:, half:], chunk,
+                       initial_states=Ha)
+    per_bh, fro = O.error_metrics(torch.cat([Ya, Yb], 1).cpu(), Y.cpu())
+    assert per_bh < 2e-2 and fro < 5e-3, (per_bh, fro)
+
+
+# ---------------------------------------------------------------- host-buffer entry point and the drop-in Model
+
+def test_host_buffer_forward_equals_device_forward():
+    W = _ssd()
+    inp = O.make_inputs(b=3, s=512, h=8, p=64, n=64, g=2, dtype=torch.bfloat16, init=True, seed=13, decay_scale=0.1)
+    d = _to_dev(inp)
+    Yd = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], 128, initial_states=d["initial_states"])
+    Yh = W.ssd_forward_host(inp["X"].pin_memory(), inp["A"].pin_memory(), inp["B"].pin_memory(),
+                            inp["C"].pin_memory(), 128, initial_states=inp["initial_states"])
+    assert not Yh.is_cuda
+    assert torch.equal(Yh, Yd.cpu())
+
+
+def test_dropin_model_matches_reference_golden(golden_dir):
+    from workloadsuite_b200 import mamba_model as M
+
+    z = np.load(golden_dir / "model_tiny.npz")
+    init = [int(v) for v in z["__init"]]
+    model = M.Model(*init).eval()
+    sd = {k: torch.from_numpy(z[k]) for k in z.files if not k.startswith("__")}
+    missing = model.load_state_dict(sd, strict=True)
+    assert not missing.missing_keys and not missing.unexpected_keys
+    model = model.to(DEV)
+    u = torch.from_numpy(z["__input"]).to(DEV)
+    with torch.inference_mode():
+        y = model(u)
+    assert y.dtype == torch.float16 and y.shape == u.shape
+    ref = torch.from_numpy(z["__output"]).double()
+    err = (y.cpu().double() - ref).abs().max().item() / ref.abs().max().item()
+    assert err < 2e-2, err
+
+
+def test_dropin_module_contract():
+    """Same checks the reference applies to its workloads (tests/test_diverse_workloads.py:61-72)."""
+    import importlib.util
+    from pathlib import Path
+
+    path = Path(__file__).resolve().parent.parent / "workloadsuite_b200" / "mamba_model.py"
+    spec = importlib.util.spec_from_file_location("ws_mamba_model", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    assert callable(mod.get_inputs) and callable(mod.get_init_inputs)
+    assert mod.get_init_inputs() == [2048, 24, 128, 128, 64, 8, 64, 4]
+    model = mod.Model(128, 1, 4, 128, 64, 2, 64, 4).to(DEV).eval()
+    x = torch.randn(2, 256, 128, dtype=torch.float16, device=DEV)
+    with torch.inference_mode():
+        y = model(x)
+        y2 = model(x)
+    assert isinstance(y, torch.Tensor) and torch.isfinite(y).all() and torch.equal(y, y2)
+    with pytest.raises(ValueError):
+        mod.SSDLayer(64, 6, 16, 64, 4)
