@@ -138,6 +138,33 @@ int ssd_b200_fold_states(const float* states, int64_t states_shard_stride, const
 size_t ssd_b200_host_scratch_bytes(const SsdArgs* host);
 int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scratch_bytes);
 
+/* Fixed size of the scratch array behind ssd_b200_forward_static_scratch(). */
+#define SSD_STATIC_SCRATCH_BYTES ((size_t)16 << 20)
+
+/* ssd_b200_forward() for callers that cannot allocate device memory and have no
+ * workspace to pass: a plugin inside a host runtime that owns the device heap
+ * and forbids cudaMalloc on its request path, or a bare FFI client without an
+ * allocator.  No counterpart in the reference (PyTorch allocates its
+ * temporaries there, model_ref.py:135-161).
+ *
+ * Same arguments and results as ssd_b200_forward(); args->workspace and
+ * args->workspace_bytes are ignored.  The scratch of the segmented scan comes
+ * from one SSD_STATIC_SCRATCH_BYTES (16 MiB) array that is part of the library
+ * image: every GPU that loads the library holds it until the process exits.
+ *   - Returns SSD_ERR_TOO_LARGE when ssd_b200_workspace_bytes(args) exceeds
+ *     that size (reduce args->nsegments, or use ssd_b200_forward()).
+ *   - Calls no cudaMalloc/cudaFree and no allocating library routine.
+ *   - The first call on each device looks the array's device address up (with
+ *     that device current) and keeps it; make that first call outside any
+ *     stream capture.
+ *   - All calls on one device share the array.  It keeps the previous call's
+ *     contents; the scan overwrites what it reads, so nothing needs clearing.
+ *     Two calls whose kernels may overlap on the GPU (different streams) race
+ *     on it: serialise them.
+ * ssd_b200_static_scratch_capacity() returns SSD_STATIC_SCRATCH_BYTES. */
+size_t ssd_b200_static_scratch_capacity(void);
+int ssd_b200_forward_static_scratch(const SsdArgs* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
