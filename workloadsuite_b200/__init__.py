@@ -5,7 +5,7 @@
 ``mamba_model``       drop-in ``Model`` / ``get_init_inputs`` / ``get_inputs`` module
 ``sharded``           head-sharded and sequence-sharded multi-GPU forwards
 """
-from .ssd import (HostRunner, SsdError, fold_states, kernel_name, plan, ssd_forward,  # noqa: F401
+from .ssd import (HostRunner, SsdError, device_status, fold_states, kernel_name, plan, ssd_forward,  # noqa: F401
                   ssd_forward_host)
 
-__all__ = ["ssd_forward", "ssd_forward_host", "HostRunner", "fold_states", "kernel_name", "plan", "SsdError"]
+__all__ = ["ssd_forward", "ssd_forward_host", "HostRunner", "fold_states", "kernel_name", "plan", "device_status", "SsdError"]

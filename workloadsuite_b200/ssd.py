@@ -18,6 +18,28 @@ _KERNELS = {None: _lib.KERNEL_AUTO, "auto": _lib.KERNEL_AUTO, "scan_f32": _lib.K
             "tcgen05": _lib.KERNEL_TCGEN05}
 
 _workspaces: dict = {}
+_status: dict = {}
+
+
+def _status_word(device) -> torch.Tensor:
+    key = (device.type, device.index)
+    st = _status.get(key)
+    if st is None:
+        st = torch.zeros(1, dtype=torch.int32, device=device)
+        _status[key] = st
+    return st
+
+
+def device_status(device="cuda:0", clear: bool = True) -> int:
+    """Synchronises and returns the kernels' status word for ``device`` (0 = fine; 1/2/3 = a bounded
+    wait on TMA / tensor-core / intra-CTA synchronisation ran out and the kernel gave up)."""
+    device = torch.device(device)
+    st = _status_word(device)
+    torch.cuda.synchronize(device)
+    v = int(st.item())
+    if clear and v:
+        st.zero_()
+    return v
 
 
 class SsdError(RuntimeError):
@@ -36,9 +58,17 @@ def _raise(code: int):
 
 
 def _strides3(t: torch.Tensor, name: str):
+    """Element strides of the three outer axes; a size-1 axis gets its contiguous stride
+    (its real stride is arbitrary and may break the 16-byte rule of TMA descriptors)."""
     if t.stride(-1) != 1 and t.shape[-1] != 1:
         raise ValueError(f"{name}: innermost axis must be contiguous")
-    return (C.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+    st = list(t.stride()[:3])
+    inner = t.shape[3]
+    for d in (2, 1, 0):
+        if t.shape[d] == 1:
+            st[d] = inner
+        inner = max(inner, st[d] * t.shape[d])
+    return (C.c_int64 * 3)(*st)
 
 
 def _check(X, A, B, Cm, dt, initial_states):
@@ -74,6 +104,7 @@ def _fill(args, X, A, B, Cm, dt, initial_states, Y, final_state, final_ld, chunk
     if kernel not in _KERNELS:
         raise ValueError(f"kernel must be one of {sorted(k for k in _KERNELS if k)}")
     args.kernel = _KERNELS[kernel]
+    args.status = _status_word(X.device).data_ptr() if X.is_cuda else None
     args.flags = _lib.FLAG_STATE_ONLY if state_only else 0
     args.nsegments = int(nsegments or 0)
     args.x_stride = _strides3(X, "X")
