@@ -328,6 +328,8 @@ def main():
     # ---- end to end through the host-buffer entry point (pinned host tensors, copies timed)
     e2e = None
     try:
+        if args.e2e_steps <= 0:
+            raise RuntimeError("skipped (--e2e-steps 0)")
         hs = {k: v.cpu().pin_memory() for k, v in sets[0].items()}
         hout = torch.empty_like(hs["X"]).pin_memory()
         runner = W.HostRunner(cfg["b"], s_loc, h_loc, cfg["p"], cfg["n"], sets[0]["B"].shape[2], chunk,
