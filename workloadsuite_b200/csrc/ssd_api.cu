@@ -2,6 +2,7 @@
 // validation, kernel choice, sequence segmentation and the host-buffer pipeline.
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "ssd_common.cuh"
@@ -44,6 +45,13 @@ int resolve_kernel(const SsdArgs* a) {
   return ssd::tc_supports(*a) ? SSD_KERNEL_TCGEN05 : SSD_KERNEL_SCAN_F32;
 }
 
+// SSD_B200_TC_VARIANT=1 forces the one-head-per-CTA tensor-core kernel (for comparisons).
+bool use_tc2(const SsdArgs* a) {
+  const char* v = std::getenv("SSD_B200_TC_VARIANT");
+  if (v && v[0] == '1') return false;
+  return ssd::tc2_supports(*a);
+}
+
 int tile_tokens(int kernel) { return kernel == SSD_KERNEL_TCGEN05 ? 128 : ssd::scan_f32_tile_tokens(); }
 
 // Number of independently scanned segments per sequence and their length.
@@ -52,7 +60,7 @@ void resolve_segments(const SsdArgs* a, int kernel, int* nseg, int* seg_len) {
   int want = a->nsegments;
   if (want <= 0) {
     if (kernel == SSD_KERNEL_TCGEN05) {
-      want = ssd::tc_default_segments(*a);
+      want = use_tc2(a) ? ssd::tc2_default_segments(*a) : ssd::tc_default_segments(*a);
     } else {
       const int64_t units = (int64_t)a->batch * a->nheads;
       // Two passes cost about 1.5x the work of one, so split only when the
@@ -92,7 +100,7 @@ void fill_params(const SsdArgs* a, ssd::ScanParams* p) {
 }
 
 int launch_kernel(int kernel, const SsdArgs* a, const ssd::ScanParams& prm, cudaStream_t stream) {
-  if (kernel == SSD_KERNEL_TCGEN05) return ssd::launch_tc(*a, prm, stream);
+  if (kernel == SSD_KERNEL_TCGEN05) return use_tc2(a) ? ssd::launch_tc2(*a, prm, stream) : ssd::launch_tc(*a, prm, stream);
   return ssd::launch_scan_f32(prm, a->dtype, stream);
 }
 

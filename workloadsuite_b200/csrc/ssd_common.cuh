@@ -72,4 +72,9 @@ bool tc_supports(const SsdArgs& a);
 int tc_default_segments(const SsdArgs& a);
 int launch_tc(const SsdArgs& a, const ScanParams& prm, cudaStream_t stream);
 
+// two-heads-per-CTA tcgen05 kernel (ssd_tc2.cu): needs an even number of heads per B/C group
+bool tc2_supports(const SsdArgs& a);
+int tc2_default_segments(const SsdArgs& a);
+int launch_tc2(const SsdArgs& a, const ScanParams& prm, cudaStream_t stream);
+
 }  // namespace ssd

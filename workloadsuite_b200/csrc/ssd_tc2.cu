@@ -1,0 +1,605 @@
+// Two-head tensor-core SSD forward for sm_100a (the fast path when the heads of a
+// group come in pairs).  One persistent CTA per SM walks (batch, head pair, segment)
+// items; inside an item it walks the 128-token tiles in order.
+//
+// The two heads of a pair read the same B and C (model_ref.py:97-99), so B, C and
+// G = C.B^T (model_ref.py:143) are loaded/computed once per tile and shared; each head
+// has its own compute warpgroup (one thread per tile row / TMEM lane) and its own
+// TMEM accumulators.  Per head and tile, in the order the warpgroup runs them:
+//   a. H <- exp(cs_last) H + S           (model_ref.py:150,156)   S = B^T.Xd from the previous step c
+//   b. Y <- exp(cs_l) * (C.H)            (model_ref.py:160-161)   scaled in place in TMEM, H copy -> smem
+//   c. next tile: prefix sum (:135), Xd = exp(cs_last - cs_l) x~ (:144,148) -> smem -> S MMA
+//   d. P = G o exp(segsum) o causal      (:139-145) -> TMEM as the A operand of Y += P.X
+//   e. Y -> global                        (:162)
+// Warp 0 is the TMA producer, warp 1 issues every tcgen05.mma from a small task
+// scheduler that polls the mbarriers (so the two heads may drift apart), warps 4-7
+// and 8-11 are the compute warpgroups.  All waits are bounded.
+#include <cuda.h>
+
+#include <algorithm>
+#include <type_traits>
+
+#include "ssd_common.cuh"
+#include "tc_common.cuh"
+#include "tc_ptx.cuh"
+
+namespace ssd {
+namespace {
+
+using namespace ptx;
+using namespace tc;
+
+constexpr int kThreads2 = 384;
+constexpr int kSms = 148;
+
+template <int N>
+struct Layout2 {
+  static constexpr int NB = N / 64;
+  static constexpr int oB = 0;
+  static constexpr int oC = oB + NB * kBlk;
+  static constexpr int oX = oC + NB * kBlk;     // [head][stage]
+  static constexpr int oXd = oX + 4 * kBlk;      // [head]
+  static constexpr int oH = oXd + 2 * kBlk;      // [head], N rows of 128 B
+  static constexpr int oMisc = oH + 2 * N * 128;
+  static constexpr int kBytes = oMisc + 4096 + 1024;
+};
+
+struct Misc2 {
+  uint64_t full_b, full_c, empty_b, empty_c;
+  uint64_t full_x[2][2], empty_x[2][2];
+  uint64_t bar_g;
+  uint64_t bar_yo[2], bar_s[2], bar_y[2];            // tcgen05.commit arrivals
+  uint64_t bar_xd[2], bar_h[2], bar_p[2], bar_e[2];  // 128 compute-thread arrivals
+  uint32_t tmem_base;
+  volatile int abort_flag;
+  float wsum[2][2][4];
+  alignas(16) float cs2[2][2][T];
+};
+
+struct Tc2Params {
+  ScanParams sp;
+  int nitems;   // (batch * nheads / 2) * nseg
+  int upairs;   // batch * nheads / 2
+};
+
+struct Item {
+  int seg, bi, h0, gi, t_begin, ntiles;
+};
+
+__device__ __forceinline__ Item decode_item(const ScanParams& sp, int upairs, int item) {
+  Item it;
+  it.seg = item / upairs;
+  const int u2 = item - it.seg * upairs;
+  const int hp = sp.nheads >> 1;
+  it.bi = u2 / hp;
+  it.h0 = 2 * (u2 - it.bi * hp);
+  it.gi = it.h0 / (sp.nheads / sp.ngroups);
+  it.t_begin = it.seg * sp.seg_len;
+  const int t_end = min(sp.seqlen, it.t_begin + sp.seg_len);
+  it.ntiles = (t_end - it.t_begin) / T;
+  return it;
+}
+
+__device__ __forceinline__ bool wait2(uint64_t* bar, uint32_t parity, Misc2* m, int code, int32_t* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  int it = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++it & 63) == 0) {
+      if (m->abort_flag) return false;
+      if (clock64() - t0 > kWaitClocks) {
+        m->abort_flag = 1;
+        if (status) atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+// Number of completed phases of `bar` observed so far is `seen`; advance it as far as
+// the barrier allows without blocking and report whether it reached `need`.
+__device__ __forceinline__ bool reached(uint64_t* bar, uint32_t& seen, uint32_t need) {
+  while (seen < need) {
+    if (!mbar_try_wait(bar, seen & 1)) return false;
+    ++seen;
+  }
+  return true;
+}
+
+template <typename T16, int N>
+__global__ void __launch_bounds__(kThreads2, 1)
+ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmC, const Tc2Params prm) {
+  using L = Layout2<N>;
+  constexpr int NB = L::NB;
+  constexpr int KN = N / 16;
+  constexpr int KT = T / 16;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  Misc2* m = reinterpret_cast<Misc2*>(smem + L::oMisc);
+  const ScanParams& sp = prm.sp;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool want_y = sp.compute_y != 0;
+  int32_t* status = sp.status;
+
+  if (tid == 0) {
+    mbar_init(&m->full_b, 1); mbar_init(&m->full_c, 1); mbar_init(&m->empty_b, 1); mbar_init(&m->empty_c, 1);
+    mbar_init(&m->bar_g, 1);
+    for (int h = 0; h < 2; ++h) {
+      for (int s = 0; s < 2; ++s) { mbar_init(&m->full_x[h][s], 1); mbar_init(&m->empty_x[h][s], 1); }
+      mbar_init(&m->bar_yo[h], 1); mbar_init(&m->bar_s[h], 1); mbar_init(&m->bar_y[h], 1);
+      mbar_init(&m->bar_xd[h], 128); mbar_init(&m->bar_h[h], 128); mbar_init(&m->bar_p[h], 128);
+      mbar_init(&m->bar_e[h], 128);
+    }
+    m->abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) tmem_alloc(&m->tmem_base, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tb = m->tmem_base;
+  const uint32_t tG = tb;
+  const uint32_t sB = smem_u32(smem + L::oB), sC = smem_u32(smem + L::oC), sX = smem_u32(smem + L::oX);
+  const uint32_t sXd = smem_u32(smem + L::oXd), sH = smem_u32(smem + L::oH);
+
+  if (warp < 4) {
+    setmaxnreg_dec<56>();   // 128*56 + 256*224 = 384*168: the CTA can only re-divide its own allocation
+    if (warp == 0 && lane == 0) {
+      // ---------------------------------------------------------------- TMA producer
+      prefetch_tmap(&tmX); prefetch_tmap(&tmB); prefetch_tmap(&tmC);
+      bool ok = true;
+      uint32_t it = 0;   // running tile ordinal of this CTA
+      for (int item = blockIdx.x; item < prm.nitems && ok; item += gridDim.x) {
+        const Item w = decode_item(sp, prm.upairs, item);
+        for (int j = 0; j < w.ntiles && ok; ++j, ++it) {
+          const int t0 = w.t_begin + j * T;
+          if (want_y) {
+            if (it > 0) ok = wait2(&m->empty_c, (it - 1) & 1, m, STATUS_WAIT_TIMEOUT_MMA, status);
+            if (!ok) break;
+            mbar_expect_tx(&m->full_c, NB * kBlk);
+#pragma unroll
+            for (int kb = 0; kb < NB; ++kb)
+              tma_load_4d(smem + L::oC + kb * kBlk, &tmC, &m->full_c, 64 * kb, w.gi, t0, w.bi);
+          }
+          if (it > 0) ok = wait2(&m->empty_b, (it - 1) & 1, m, STATUS_WAIT_TIMEOUT_MMA, status);
+          if (!ok) break;
+          mbar_expect_tx(&m->full_b, NB * kBlk);
+#pragma unroll
+          for (int kb = 0; kb < NB; ++kb)
+            tma_load_4d(smem + L::oB + kb * kBlk, &tmB, &m->full_b, 64 * kb, w.gi, t0, w.bi);
+          const int st = it & 1;
+          for (int h = 0; h < 2 && ok; ++h) {
+            if (it >= 2) ok = wait2(&m->empty_x[h][st], ((it - 2) >> 1) & 1, m, STATUS_WAIT_TIMEOUT_MMA, status);
+            if (!ok) break;
+            mbar_expect_tx(&m->full_x[h][st], kBlk);
+            tma_load_4d(smem + L::oX + (2 * h + st) * kBlk, &tmX, &m->full_x[h][st], 0, w.h0 + h, t0, w.bi);
+          }
+        }
+      }
+      if (m->abort_flag && it > 0) {
+        // let copies already in flight land before the CTA gives its shared memory back
+        const uint32_t k = it - 1;
+        const long long c0 = clock64();
+        while (clock64() - c0 < 2000000LL) {
+          if (mbar_try_wait(&m->full_b, k & 1) && mbar_try_wait(&m->full_x[0][k & 1], (k >> 1) & 1) &&
+              mbar_try_wait(&m->full_x[1][k & 1], (k >> 1) & 1) && (!want_y || mbar_try_wait(&m->full_c, k & 1)))
+            break;
+        }
+      }
+    } else if (warp == 1 && lane == 0) {
+      // ---------------------------------------------------------------- MMA task scheduler
+      constexpr int fmt = std::is_same<T16, __nv_bfloat16>::value ? 1 : 0;
+      constexpr uint32_t idG = umma_idesc(128, 128, fmt, 0, 0);
+      constexpr uint32_t idKM = umma_idesc(128, 64, fmt, 0, 1);
+      constexpr uint32_t idMM = umma_idesc(128, 64, fmt, 1, 1);
+      constexpr uint64_t dK = umma_desc_base(16, 1024);
+      constexpr uint64_t dMN = umma_desc_base(kBlk, 1024);
+      uint32_t ttot = 0;
+      for (int item = blockIdx.x; item < prm.nitems; item += gridDim.x) ttot += decode_item(sp, prm.upairs, item).ntiles;
+      uint32_t nG = 0, relC = 0, relB = 0;
+      uint32_t nYo[2] = {0, 0}, nS[2] = {0, 0}, nYd[2] = {0, 0};
+      uint32_t seenFC = 0, seenFB = 0;
+      uint32_t seenP[2] = {0, 0}, seenH[2] = {0, 0}, seenE[2] = {0, 0}, seenXd[2] = {0, 0};
+      uint32_t seenFX[2][2] = {{0, 0}, {0, 0}};
+      long long last_progress = clock64();
+      while (true) {
+        const bool done = want_y ? (nYd[0] == ttot && nYd[1] == ttot) : (nS[0] == ttot && nS[1] == ttot);
+        if (done) break;
+        bool progress = false;
+        if (want_y) {
+          // G(k): both heads are done reading G(k-1); B and C of tile k have landed
+          if (nG < ttot && reached(&m->bar_p[0], seenP[0], nG) && reached(&m->bar_p[1], seenP[1], nG) &&
+              reached(&m->full_c, seenFC, nG + 1) && reached(&m->full_b, seenFB, nG + 1)) {
+            tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < KN; ++k) {
+              const uint32_t off = (k >> 2) * kBlk + (k & 3) * 32;
+              umma_ss(tG, umma_desc(dK, sC + off), umma_desc(dK, sB + off), idG, k > 0);
+            }
+            umma_commit(&m->bar_g);
+            ++nG;
+            progress = true;
+          }
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint32_t tY = tb + 128 + 192 * h + 128;
+            // Yo(k): state copy in place, previous Y tile read out, C landed
+            if (nYo[h] < ttot && reached(&m->full_c, seenFC, nYo[h] + 1) && reached(&m->bar_h[h], seenH[h], nYo[h] + 1) &&
+                reached(&m->bar_e[h], seenE[h], nYo[h])) {
+              tc_fence_after();
+#pragma unroll
+              for (int k = 0; k < KN; ++k) {
+                const uint32_t off = (k >> 2) * kBlk + (k & 3) * 32;
+                umma_ss(tY, umma_desc(dK, sC + off), umma_desc(dMN, sH + h * (N * 128) + k * 2048), idKM, k > 0);
+              }
+              umma_commit(&m->bar_yo[h]);
+              ++nYo[h];
+              progress = true;
+            }
+          }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t tS = tb + 128 + 192 * h;
+          if (nS[h] < ttot && reached(&m->full_b, seenFB, nS[h] + 1) && reached(&m->bar_xd[h], seenXd[h], nS[h] + 1)) {
+            tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < KT; ++k)
+              umma_ss(tS, umma_desc(dMN, sB + k * 2048), umma_desc(dMN, sXd + h * kBlk + k * 2048), idMM, k > 0);
+            umma_commit(&m->bar_s[h]);
+            if (!want_y) mbar_arrive(&m->empty_x[h][nS[h] & 1]);   // X was only read by the compute warps
+            ++nS[h];
+            progress = true;
+          }
+        }
+        if (want_y) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint32_t tP = tb + 128 + 192 * h + 64, tY = tb + 128 + 192 * h + 128;
+            const uint32_t k0 = nYd[h], st = k0 & 1;
+            if (k0 < ttot && reached(&m->bar_p[h], seenP[h], k0 + 1) &&
+                reached(&m->full_x[h][st], seenFX[h][st], (k0 >> 1) + 1)) {
+              tc_fence_after();
+#pragma unroll
+              for (int k = 0; k < KT; ++k)
+                umma_ts(tY, tP + 8 * k, umma_desc(dMN, sX + (2 * h + st) * kBlk + k * 2048), idKM, 1);
+              umma_commit(&m->bar_y[h]);
+              umma_commit(&m->empty_x[h][st]);
+              ++nYd[h];
+              progress = true;
+            }
+          }
+          const uint32_t cdone = min(nG, min(nYo[0], nYo[1]));
+          if (relC < cdone) { umma_commit(&m->empty_c); ++relC; progress = true; }
+        }
+        const uint32_t bdone = want_y ? min(nG, min(nS[0], nS[1])) : min(nS[0], nS[1]);
+        if (relB < bdone) { umma_commit(&m->empty_b); ++relB; progress = true; }
+        if (progress) {
+          last_progress = clock64();
+        } else {
+          if (m->abort_flag) break;
+          if (clock64() - last_progress > kWaitClocks) {
+            m->abort_flag = 1;
+            if (status) atomicCAS(status, 0, (int)STATUS_WAIT_TIMEOUT_SYNC);
+            break;
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ compute warpgroups (warps 4-7: head 0, 8-11: head 1)
+    setmaxnreg_inc<224>();
+    const int h = (warp - 4) >> 2;
+    const int lane_base = (warp & 3) * 32;
+    const int l = lane_base + lane;
+    const int q = warp & 3;
+    const uint32_t tlane = (uint32_t)lane_base << 16;
+    const uint32_t swz = (uint32_t)(l & 7);
+    const bool owns_state = lane_base < N;
+    const uint32_t tS = tb + 128 + 192 * h, tP = tS + 64, tY = tS + 128;
+    const uint32_t sHh = sH + h * (N * 128), sXdh = sXd + h * kBlk;
+    const int bar_id = 1 + h;
+
+    uint32_t it = 0;   // running tile ordinal of this CTA
+    bool ok = true;
+    auto cwait = [&](uint64_t* bar, uint32_t parity, int code) {
+      return __all_sync(0xffffffffu, wait2(bar, parity, m, code, status)) != 0;
+    };
+
+    float H[P];
+    float cs = 0.f, tot = 0.f, cs2 = 0.f;   // of the tile whose P / Y is being produced
+    double asum = 0.0;
+
+    // prefix sum of the log-decay over the 128 rows (model_ref.py:135); publishes cs*log2(e) for the P step
+    auto scan_tile = [&](float a, uint32_t par, float& cs_o, float& tot_o, float& cs2_o) {
+      float v = a;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const float t = __shfl_up_sync(0xffffffffu, v, d);
+        if (lane >= d) v += t;
+      }
+      if (lane == 31) m->wsum[h][par][q] = v;
+      named_bar_sync(bar_id, 128);
+      const float w0 = m->wsum[h][par][0], w1 = m->wsum[h][par][1], w2 = m->wsum[h][par][2], w3 = m->wsum[h][par][3];
+      cs_o = v + ((q > 0 ? w0 : 0.f) + (q > 1 ? w1 : 0.f) + (q > 2 ? w2 : 0.f));
+      tot_o = (w0 + w1 + w2) + w3;
+      cs2_o = cs_o * kLog2e;
+      m->cs2[h][par][l] = cs2_o;
+      named_bar_sync(bar_id, 128);
+    };
+    // Xd = exp(cs_last - cs_l) * x~ (model_ref.py:144,148) from X stage `st` into this head's Xd buffer
+    auto make_xd = [&](uint32_t st, float cs_t, float tot_t, float dtv, bool has_dt) {
+      const float dl = ex2((tot_t - cs_t) * kLog2e);
+      const uint32_t xrow = sX + (2 * h + st) * kBlk + l * 128, xdrow = sXdh + l * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint32_t phys = (c ^ swz) << 4;
+        uint4 raw = lds128(xrow + phys);
+        float2 f0 = unpack2<T16>(raw.x), f1 = unpack2<T16>(raw.y), f2 = unpack2<T16>(raw.z), f3 = unpack2<T16>(raw.w);
+        if (has_dt) {
+          f0.x *= dtv; f0.y *= dtv; f1.x *= dtv; f1.y *= dtv; f2.x *= dtv; f2.y *= dtv; f3.x *= dtv; f3.y *= dtv;
+          raw.x = pack2<T16>(f0.x, f0.y); raw.y = pack2<T16>(f1.x, f1.y);
+          raw.z = pack2<T16>(f2.x, f2.y); raw.w = pack2<T16>(f3.x, f3.y);
+          sts128(xrow + phys, raw);
+        }
+        uint4 o;
+        o.x = pack2<T16>(f0.x * dl, f0.y * dl); o.y = pack2<T16>(f1.x * dl, f1.y * dl);
+        o.z = pack2<T16>(f2.x * dl, f2.y * dl); o.w = pack2<T16>(f3.x * dl, f3.y * dl);
+        sts128(xdrow + phys, o);
+      }
+    };
+    auto store_hb = [&]() {
+      if (owns_state) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint4 v;
+          v.x = pack2<T16>(H[8 * c + 0], H[8 * c + 1]); v.y = pack2<T16>(H[8 * c + 2], H[8 * c + 3]);
+          v.z = pack2<T16>(H[8 * c + 4], H[8 * c + 5]); v.w = pack2<T16>(H[8 * c + 6], H[8 * c + 7]);
+          sts128(sHh + l * 128 + ((c ^ swz) << 4), v);
+        }
+      }
+    };
+
+    for (int item = blockIdx.x; item < prm.nitems && ok; item += gridDim.x) {
+      const Item w = decode_item(sp, prm.upairs, item);
+      if (w.ntiles == 0) continue;
+      const int hi = w.h0 + h;
+      const int64_t unit = (int64_t)w.bi * sp.nheads + hi;
+      const float* Ag = sp.A + w.bi * sp.as[0] + hi * sp.as[2];
+      const T16* Dg = sp.dt ? static_cast<const T16*>(sp.dt) + w.bi * sp.dts[0] + hi * sp.dts[2] : nullptr;
+      T16* Yg = want_y ? static_cast<T16*>(sp.Y) + w.bi * sp.ys[0] + hi * sp.ys[2] : nullptr;
+
+      // ---- state entering the item
+      if (sp.init && owns_state) {
+        const float4* I = reinterpret_cast<const float4*>(sp.init + unit * sp.init_unit_stride +
+                                                          w.seg * sp.init_seg_stride + (int64_t)l * P);
+#pragma unroll
+        for (int j = 0; j < P / 4; ++j) {
+          const float4 v = I[j];
+          H[4 * j] = v.x; H[4 * j + 1] = v.y; H[4 * j + 2] = v.z; H[4 * j + 3] = v.w;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < P; ++j) H[j] = 0.f;
+      }
+      asum = 0.0;
+      if (want_y) {
+        // the previous item's last C.H may still be reading this buffer
+        if (it > 0) { ok = cwait(&m->bar_yo[h], (it - 1) & 1, STATUS_WAIT_TIMEOUT_MMA); if (!ok) break; }
+        store_hb();
+        fence_proxy_async();
+        mbar_arrive(&m->bar_h[h]);
+      }
+      // ---- first tile of the item: prefix sum and Xd
+      float a_next = Ag[(int64_t)(w.t_begin + l) * sp.as[1]];
+      float dt_next = Dg ? Cvt<T16>::to_f(Dg[(int64_t)(w.t_begin + l) * sp.dts[1]]) : 1.f;
+      {
+        const float a = a_next, dtv = dt_next;
+        if (w.ntiles > 1) {
+          a_next = Ag[(int64_t)(w.t_begin + T + l) * sp.as[1]];
+          if (Dg) dt_next = Cvt<T16>::to_f(Dg[(int64_t)(w.t_begin + T + l) * sp.dts[1]]);
+        }
+        // the previous S MMA of this head must be done with the Xd buffer
+        if (it > 0) { ok = cwait(&m->bar_s[h], (it - 1) & 1, STATUS_WAIT_TIMEOUT_MMA); if (!ok) break; }
+        scan_tile(a, it & 1, cs, tot, cs2);
+        ok = cwait(&m->full_x[h][it & 1], (it >> 1) & 1, STATUS_WAIT_TIMEOUT_TMA);
+        if (!ok) break;
+        make_xd(it & 1, cs, tot, dtv, Dg != nullptr);
+        fence_proxy_async();
+        mbar_arrive(&m->bar_xd[h]);
+      }
+
+      for (int j = 0; j < w.ntiles && ok; ++j, ++it) {
+        const int t0 = w.t_begin + j * T;
+        const bool last = (j + 1 == w.ntiles);
+        // ---- a. state: H <- exp(cs_last) H + S
+        ok = cwait(&m->bar_s[h], it & 1, STATUS_WAIT_TIMEOUT_MMA);
+        if (!ok) break;
+        tc_fence_after();
+        asum += (double)tot;
+        if (owns_state) {
+          const float g = ex2(tot * kLog2e);
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            uint32_t sv[32];
+            tmem_ld32(tS + tlane + 32 * hf, sv);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) H[32 * hf + e] = fmaf(H[32 * hf + e], g, __uint_as_float(sv[e]));
+          }
+        }
+        if (want_y) {
+          // ---- b. Y <- exp(cs_l) * (C.H) in place; the MMA of step d accumulates P.X on top
+          ok = cwait(&m->bar_yo[h], it & 1, STATUS_WAIT_TIMEOUT_MMA);
+          if (!ok) break;
+          tc_fence_after();
+          const float el = ex2(cs2);
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            uint32_t yv[32];
+            tmem_ld32(tY + tlane + 32 * hf, yv);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) yv[e] = __float_as_uint(__uint_as_float(yv[e]) * el);
+            tmem_st32(tY + tlane + 32 * hf, yv);
+          }
+          tmem_st_wait();
+          if (!last) {
+            store_hb();
+            fence_proxy_async();
+            mbar_arrive(&m->bar_h[h]);
+          }
+        }
+        // ---- c. next tile: prefix sum and Xd (its S MMA then overlaps steps d and e)
+        float cs_n = 0.f, tot_n = 0.f, cs2_n = 0.f;
+        if (!last) {
+          const float a = a_next, dtv = dt_next;
+          if (j + 2 < w.ntiles) {
+            a_next = Ag[(int64_t)(t0 + 2 * T + l) * sp.as[1]];
+            if (Dg) dt_next = Cvt<T16>::to_f(Dg[(int64_t)(t0 + 2 * T + l) * sp.dts[1]]);
+          }
+          scan_tile(a, (it + 1) & 1, cs_n, tot_n, cs2_n);
+          ok = cwait(&m->full_x[h][(it + 1) & 1], ((it + 1) >> 1) & 1, STATUS_WAIT_TIMEOUT_TMA);
+          if (!ok) break;
+          make_xd((it + 1) & 1, cs_n, tot_n, dtv, Dg != nullptr);
+          fence_proxy_async();
+          mbar_arrive(&m->bar_xd[h]);
+        }
+        if (want_y) {
+          // ---- d. P = (C B^T) o exp(segsum), causal -> TMEM (A operand, 16-bit pairs)
+          ok = cwait(&m->bar_g, it & 1, STATUS_WAIT_TIMEOUT_MMA);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t par = it & 1;
+#pragma unroll
+          for (int jc = 0; jc < 4; ++jc) {
+            uint32_t pk[16];
+            if (jc > q) {
+#pragma unroll
+              for (int e = 0; e < 16; ++e) pk[e] = 0u;
+            } else {
+              uint32_t gv[32];
+              tmem_ld32(tG + tlane + 32 * jc, gv);
+              tmem_ld_wait();
+              const float4* csv = reinterpret_cast<const float4*>(&m->cs2[h][par][32 * jc]);
+#pragma unroll
+              for (int e4 = 0; e4 < 8; ++e4) {
+                const float4 c4 = csv[e4];
+                const float cc[4] = {c4.x, c4.y, c4.z, c4.w};
+                float pv[4];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                  const int e = 4 * e4 + r;
+                  const float val = __uint_as_float(gv[e]) * ex2(cs2 - cc[r]);
+                  pv[r] = (jc < q || 32 * jc + e <= l) ? val : 0.f;
+                }
+                pk[2 * e4] = pack2<T16>(pv[0], pv[1]);
+                pk[2 * e4 + 1] = pack2<T16>(pv[2], pv[3]);
+              }
+            }
+            tmem_st16(tP + tlane + 16 * jc, pk);
+          }
+          tmem_st_wait();
+          tc_fence_before();
+          mbar_arrive(&m->bar_p[h]);
+
+          // ---- e. Y -> global
+          ok = cwait(&m->bar_y[h], it & 1, STATUS_WAIT_TIMEOUT_MMA);
+          if (!ok) break;
+          tc_fence_after();
+          T16* yrow = Yg + (int64_t)(t0 + l) * sp.ys[1];
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            uint32_t yv[32];
+            tmem_ld32(tY + tlane + 32 * hf, yv);
+            tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint4 o;
+              o.x = pack2<T16>(__uint_as_float(yv[8 * c + 0]), __uint_as_float(yv[8 * c + 1]));
+              o.y = pack2<T16>(__uint_as_float(yv[8 * c + 2]), __uint_as_float(yv[8 * c + 3]));
+              o.z = pack2<T16>(__uint_as_float(yv[8 * c + 4]), __uint_as_float(yv[8 * c + 5]));
+              o.w = pack2<T16>(__uint_as_float(yv[8 * c + 6]), __uint_as_float(yv[8 * c + 7]));
+              *reinterpret_cast<uint4*>(yrow + 32 * hf + 8 * c) = o;
+            }
+          }
+          tc_fence_before();
+          mbar_arrive(&m->bar_e[h]);
+        }
+        cs = cs_n; tot = tot_n; cs2 = cs2_n;
+      }
+      if (!ok) break;
+
+      // ---- state leaving the item
+      if (sp.fin && owns_state) {
+        float4* F = reinterpret_cast<float4*>(sp.fin + unit * sp.fin_unit_stride + w.seg * sp.fin_seg_stride +
+                                              (int64_t)l * P);
+#pragma unroll
+        for (int j = 0; j < P / 4; ++j) F[j] = make_float4(H[4 * j], H[4 * j + 1], H[4 * j + 2], H[4 * j + 3]);
+      }
+      if (sp.fin_ld && l == 0) sp.fin_ld[unit * sp.finld_unit_stride + w.seg * sp.finld_seg_stride] = (float)asum;
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    __syncwarp();
+    tmem_dealloc(tb, 512);
+  }
+}
+
+template <typename T16, int N>
+int launch_typed2(const CUtensorMap& tx, const CUtensorMap& tb, const CUtensorMap& tc, const Tc2Params& prm,
+                  cudaStream_t stream) {
+  auto kern = ssd_tc2_kernel<T16, N>;
+  constexpr int smem = Layout2<N>::kBytes;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    return SSD_ERR_CUDA;
+  const int grid = std::min(prm.nitems, kSms);
+  kern<<<grid, kThreads2, smem, stream>>>(tx, tb, tc, prm);
+  return cudaGetLastError() == cudaSuccess ? SSD_OK : SSD_ERR_CUDA;
+}
+
+}  // namespace
+
+bool tc2_supports(const SsdArgs& a) {
+  if (!tc_supports(a)) return false;
+  const int hpg = a.nheads / a.ngroups;
+  return a.nheads % 2 == 0 && hpg % 2 == 0;
+}
+
+int tc2_default_segments(const SsdArgs& a) {
+  const int64_t upairs = (int64_t)a.batch * a.nheads / 2;
+  if (upairs >= 100) return 1;
+  const int tiles = a.seqlen / T;
+  int want = (int)((2 * kSms + upairs - 1) / upairs);
+  want = std::min(want, std::max(1, tiles / 4));
+  return std::max(1, want);
+}
+
+int launch_tc2(const SsdArgs& a, const ScanParams& sp, cudaStream_t stream) {
+  if (sp.seg_len % T != 0) return SSD_ERR_UNSUPPORTED;
+  Tc2Params prm;
+  prm.sp = sp;
+  prm.upairs = a.batch * (a.nheads / 2);
+  prm.nitems = prm.upairs * sp.nseg;
+  CUtensorMap tx, tb, tc;
+  if (!make_map(&tx, a.X, a.dtype, a.headdim, a.nheads, a.seqlen, a.batch, a.x_stride)) return SSD_ERR_CUDA;
+  if (!make_map(&tb, a.B, a.dtype, a.dstate, a.ngroups, a.seqlen, a.batch, a.b_stride)) return SSD_ERR_CUDA;
+  if (sp.compute_y) {
+    if (!make_map(&tc, a.C, a.dtype, a.dstate, a.ngroups, a.seqlen, a.batch, a.c_stride)) return SSD_ERR_CUDA;
+  } else {
+    tc = tb;
+  }
+  if (a.dtype == SSD_DTYPE_BF16)
+    return a.dstate == 128 ? launch_typed2<__nv_bfloat16, 128>(tx, tb, tc, prm, stream)
+                           : launch_typed2<__nv_bfloat16, 64>(tx, tb, tc, prm, stream);
+  return a.dstate == 128 ? launch_typed2<__half, 128>(tx, tb, tc, prm, stream)
+                         : launch_typed2<__half, 64>(tx, tb, tc, prm, stream);
+}
+
+}  // namespace ssd
