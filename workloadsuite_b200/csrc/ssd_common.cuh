@@ -16,7 +16,8 @@ enum : int {
   STATUS_WAIT_TIMEOUT_TMA = 1,   // a bounded wait for a TMA transfer ran out
   STATUS_WAIT_TIMEOUT_MMA = 2,   // a bounded wait for a tcgen05 commit ran out
   STATUS_WAIT_TIMEOUT_SYNC = 3,  // a bounded wait between warps of one CTA ran out
-  STATUS_TMEM_ALLOC = 4          // tensor memory could not be allocated
+  STATUS_TMEM_ALLOC = 4,         // tensor memory could not be allocated
+  STATUS_BAD_SMEM_ALIGNMENT = 5  // dynamic shared memory did not start on a 1024-byte boundary
 };
 
 // One launch of a scan over [seg_begin, seg_end) of every (batch, head) unit.

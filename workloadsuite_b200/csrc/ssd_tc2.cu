@@ -11,9 +11,10 @@
 //   c. next tile: prefix sum (:135), Xd = exp(cs_last - cs_l) x~ (:144,148) -> smem -> S MMA
 //   d. P = G o exp(segsum) o causal      (:139-145) -> TMEM as the A operand of Y += P.X
 //   e. Y -> global                        (:162)
-// Warp 0 is the TMA producer, warp 1 issues every tcgen05.mma from a small task
-// scheduler that polls the mbarriers (so the two heads may drift apart), warps 4-7
-// and 8-11 are the compute warpgroups.  All waits are bounded.
+// Warp 0 is the TMA producer, warp 1 issues the shared G MMAs, warps 2 and 3 issue the
+// per-head MMAs (one thread each, blocking on the mbarriers in the order its head's
+// warpgroup raises them, so the two heads may drift apart), warps 4-7 and 8-11 are
+// the compute warpgroups.  All waits are bounded.
 #include <cuda.h>
 
 #include <algorithm>
@@ -31,30 +32,37 @@ using namespace tc;
 
 constexpr int kThreads2 = 384;
 constexpr int kSms = 148;
+constexpr int kXStages = 3;   // X tiles in flight per head; a consumed stage doubles as the Y staging buffer
 
 template <int N>
 struct Layout2 {
   static constexpr int NB = N / 64;
   static constexpr int oB = 0;
   static constexpr int oC = oB + NB * kBlk;
-  static constexpr int oX = oC + NB * kBlk;     // [head][stage]
-  static constexpr int oXd = oX + 4 * kBlk;      // [head]
+  static constexpr int oX = oC + NB * kBlk;     // [head][stage], kXStages stages
+  static constexpr int oXd = oX + 2 * kXStages * kBlk;   // [head]
   static constexpr int oH = oXd + 2 * kBlk;      // [head], N rows of 128 B
   static constexpr int oMisc = oH + 2 * N * 128;
-  static constexpr int kBytes = oMisc + 4096 + 1024;
+  static constexpr int kBytes = oMisc + 2560;   // no slack: the dynamic segment must start 1024-byte aligned
 };
 
 struct Misc2 {
   uint64_t full_b, full_c, empty_b, empty_c;
-  uint64_t full_x[2][2], empty_x[2][2];
+  uint64_t full_x[2][kXStages], empty_x[2][kXStages];
   uint64_t bar_g;
   uint64_t bar_yo[2], bar_s[2], bar_y[2];            // tcgen05.commit arrivals
   uint64_t bar_xd[2], bar_h[2], bar_p[2], bar_e[2];  // 128 compute-thread arrivals
   uint32_t tmem_base;
   volatile int abort_flag;
-  float wsum[2][2][4];
-  alignas(16) float cs2[2][2][T];
+  float wsum[2][4];
+  // Single-buffered: they are rewritten in step c, behind a warpgroup barrier that every warp reaches only
+  // after its step d (the only reader) of the current tile.
+  alignas(16) float cs2[2][T];   // [head][row]: prefix sum of the log-decay times log2(e)
+  alignas(16) float cf[2][T];    // [head][row]: exp(cs of the row's 32-block end - cs of the row)
 };
+
+static_assert(sizeof(Misc2) <= 2560, "Misc2 outgrew its shared-memory slot");
+static_assert(Layout2<128>::kBytes <= 232448, "shared memory budget of one SM exceeded");
 
 struct Tc2Params {
   ScanParams sp;
@@ -80,29 +88,16 @@ __device__ __forceinline__ Item decode_item(const ScanParams& sp, int upairs, in
   return it;
 }
 
+// Deliberately not inlined: the kernel's steady-state loop has to stay small enough for the instruction cache.
 __device__ __forceinline__ bool wait2(uint64_t* bar, uint32_t parity, Misc2* m, int code, int32_t* status) {
-  if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  int it = 0;
-  while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++it & 63) == 0) {
-      if (m->abort_flag) return false;
-      if (clock64() - t0 > kWaitClocks) {
-        m->abort_flag = 1;
-        if (status) atomicCAS(status, 0, code);
-        return false;
-      }
+  while (!mbar_try_wait_sleep(bar, parity, 200000u)) {
+    if (m->abort_flag) return false;
+    if (clock64() - t0 > kWaitClocks) {
+      m->abort_flag = 1;
+      if (status) atomicCAS(status, 0, code);
+      return false;
     }
-  }
-}
-
-// Number of completed phases of `bar` observed so far is `seen`; advance it as far as
-// the barrier allows without blocking and report whether it reached `need`.
-__device__ __forceinline__ bool reached(uint64_t* bar, uint32_t& seen, uint32_t need) {
-  while (seen < need) {
-    if (!mbar_try_wait(bar, seen & 1)) return false;
-    ++seen;
   }
   return true;
 }
@@ -115,19 +110,26 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   constexpr int NB = L::NB;
   constexpr int KN = N / 16;
   constexpr int KT = T / 16;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
   Misc2* m = reinterpret_cast<Misc2*>(smem + L::oMisc);
   const ScanParams& sp = prm.sp;
+  if (smem_u32(smem) & 1023u) {   // the 128-byte swizzle needs 1024-byte aligned tiles; give up cleanly otherwise
+    if (threadIdx.x == 0 && sp.status) atomicCAS(sp.status, 0, (int)STATUS_BAD_SMEM_ALIGNMENT);
+    return;
+  }
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool want_y = sp.compute_y != 0;
   int32_t* status = sp.status;
 
   if (tid == 0) {
-    mbar_init(&m->full_b, 1); mbar_init(&m->full_c, 1); mbar_init(&m->empty_b, 1); mbar_init(&m->empty_c, 1);
+    mbar_init(&m->full_b, 1); mbar_init(&m->full_c, 1);
+    // B is released by the G issuer and both heads' S; C by the G issuer and both heads' C.H
+    mbar_init(&m->empty_b, want_y ? 3 : 2); mbar_init(&m->empty_c, 3);
     mbar_init(&m->bar_g, 1);
     for (int h = 0; h < 2; ++h) {
-      for (int s = 0; s < 2; ++s) { mbar_init(&m->full_x[h][s], 1); mbar_init(&m->empty_x[h][s], 1); }
+      // an X stage is handed back by the 128 threads of the head's warpgroup (after they have used it to stage Y)
+      for (int s = 0; s < kXStages; ++s) { mbar_init(&m->full_x[h][s], 1); mbar_init(&m->empty_x[h][s], 128); }
       mbar_init(&m->bar_yo[h], 1); mbar_init(&m->bar_s[h], 1); mbar_init(&m->bar_y[h], 1);
       mbar_init(&m->bar_xd[h], 128); mbar_init(&m->bar_h[h], 128); mbar_init(&m->bar_p[h], 128);
       mbar_init(&m->bar_e[h], 128);
@@ -145,7 +147,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   const uint32_t sXd = smem_u32(smem + L::oXd), sH = smem_u32(smem + L::oH);
 
   if (warp < 4) {
-    setmaxnreg_dec<56>();   // 128*56 + 256*224 = 384*168: the CTA can only re-divide its own allocation
+    setmaxnreg_dec<72>();   // 128*72 + 256*216 = 384*168: the CTA can only re-divide its own allocation
     if (warp == 0 && lane == 0) {
       // ---------------------------------------------------------------- TMA producer
       prefetch_tmap(&tmX); prefetch_tmap(&tmB); prefetch_tmap(&tmC);
@@ -155,6 +157,14 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         const Item w = decode_item(sp, prm.upairs, item);
         for (int j = 0; j < w.ntiles && ok; ++j, ++it) {
           const int t0 = w.t_begin + j * T;
+          const uint32_t st = it % kXStages, use = it / kXStages;
+          for (int h = 0; h < 2 && ok; ++h) {
+            if (use > 0) ok = wait2(&m->empty_x[h][st], (use - 1) & 1, m, STATUS_WAIT_TIMEOUT_SYNC, status);
+            if (!ok) break;
+            mbar_expect_tx(&m->full_x[h][st], kBlk);
+            tma_load_4d(smem + L::oX + (kXStages * h + st) * kBlk, &tmX, &m->full_x[h][st], 0, w.h0 + h, t0, w.bi);
+          }
+          if (!ok) break;
           if (want_y) {
             if (it > 0) ok = wait2(&m->empty_c, (it - 1) & 1, m, STATUS_WAIT_TIMEOUT_MMA, status);
             if (!ok) break;
@@ -169,13 +179,6 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 #pragma unroll
           for (int kb = 0; kb < NB; ++kb)
             tma_load_4d(smem + L::oB + kb * kBlk, &tmB, &m->full_b, 64 * kb, w.gi, t0, w.bi);
-          const int st = it & 1;
-          for (int h = 0; h < 2 && ok; ++h) {
-            if (it >= 2) ok = wait2(&m->empty_x[h][st], ((it - 2) >> 1) & 1, m, STATUS_WAIT_TIMEOUT_MMA, status);
-            if (!ok) break;
-            mbar_expect_tx(&m->full_x[h][st], kBlk);
-            tma_load_4d(smem + L::oX + (2 * h + st) * kBlk, &tmX, &m->full_x[h][st], 0, w.h0 + h, t0, w.bi);
-          }
         }
       }
       if (m->abort_flag && it > 0) {
@@ -183,114 +186,107 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         const uint32_t k = it - 1;
         const long long c0 = clock64();
         while (clock64() - c0 < 2000000LL) {
-          if (mbar_try_wait(&m->full_b, k & 1) && mbar_try_wait(&m->full_x[0][k & 1], (k >> 1) & 1) &&
-              mbar_try_wait(&m->full_x[1][k & 1], (k >> 1) & 1) && (!want_y || mbar_try_wait(&m->full_c, k & 1)))
+          const uint32_t xs = k % kXStages, xp = (k / kXStages) & 1;
+          if (mbar_try_wait(&m->full_b, k & 1) && mbar_try_wait(&m->full_x[0][xs], xp) &&
+              mbar_try_wait(&m->full_x[1][xs], xp) && (!want_y || mbar_try_wait(&m->full_c, k & 1)))
             break;
         }
       }
     } else if (warp == 1 && lane == 0) {
-      // ---------------------------------------------------------------- MMA task scheduler
+      // ---------------------------------------------------------------- MMA issuer for G = C.B^T (shared by the heads)
+      if (want_y) {
+        constexpr int fmt = std::is_same<T16, __nv_bfloat16>::value ? 1 : 0;
+        constexpr uint32_t idG = umma_idesc(128, 128, fmt, 0, 0);
+        constexpr uint64_t dK = umma_desc_base(16, 1024);
+        uint32_t ttot = 0;
+        for (int item = blockIdx.x; item < prm.nitems; item += gridDim.x)
+          ttot += decode_item(sp, prm.upairs, item).ntiles;
+        bool ok = true;
+        for (uint32_t k = 0; k < ttot && ok; ++k) {
+          // both heads are done reading G(k-1); B and C of tile k have landed
+          if (k > 0)
+            ok = wait2(&m->bar_p[0], (k - 1) & 1, m, STATUS_WAIT_TIMEOUT_SYNC, status) &&
+                 wait2(&m->bar_p[1], (k - 1) & 1, m, STATUS_WAIT_TIMEOUT_SYNC, status);
+          ok = ok && wait2(&m->full_c, k & 1, m, STATUS_WAIT_TIMEOUT_TMA, status) &&
+               wait2(&m->full_b, k & 1, m, STATUS_WAIT_TIMEOUT_TMA, status);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < KN; ++kk) {
+            const uint32_t off = (kk >> 2) * kBlk + (kk & 3) * 32;
+            umma_ss(tG, umma_desc(dK, sC + off), umma_desc(dK, sB + off), idG, kk > 0);
+          }
+          umma_commit(&m->bar_g);
+          umma_commit(&m->empty_c);
+          umma_commit(&m->empty_b);
+        }
+      }
+    } else if ((warp == 2 || warp == 3) && lane == 0) {
+      // ---------------------------------------------------------------- per-head MMA issuer: Yo, S, Yd of head h
+      // Blocking waits, in the order the head's compute warpgroup raises the barriers.
+      const int h = warp - 2;
       constexpr int fmt = std::is_same<T16, __nv_bfloat16>::value ? 1 : 0;
-      constexpr uint32_t idG = umma_idesc(128, 128, fmt, 0, 0);
       constexpr uint32_t idKM = umma_idesc(128, 64, fmt, 0, 1);
       constexpr uint32_t idMM = umma_idesc(128, 64, fmt, 1, 1);
       constexpr uint64_t dK = umma_desc_base(16, 1024);
       constexpr uint64_t dMN = umma_desc_base(kBlk, 1024);
-      uint32_t ttot = 0;
-      for (int item = blockIdx.x; item < prm.nitems; item += gridDim.x) ttot += decode_item(sp, prm.upairs, item).ntiles;
-      uint32_t nG = 0, relC = 0, relB = 0;
-      uint32_t nYo[2] = {0, 0}, nS[2] = {0, 0}, nYd[2] = {0, 0};
-      uint32_t seenFC = 0, seenFB = 0;
-      uint32_t seenP[2] = {0, 0}, seenH[2] = {0, 0}, seenE[2] = {0, 0}, seenXd[2] = {0, 0};
-      uint32_t seenFX[2][2] = {{0, 0}, {0, 0}};
-      long long last_progress = clock64();
-      while (true) {
-        const bool done = want_y ? (nYd[0] == ttot && nYd[1] == ttot) : (nS[0] == ttot && nS[1] == ttot);
-        if (done) break;
-        bool progress = false;
-        if (want_y) {
-          // G(k): both heads are done reading G(k-1); B and C of tile k have landed
-          if (nG < ttot && reached(&m->bar_p[0], seenP[0], nG) && reached(&m->bar_p[1], seenP[1], nG) &&
-              reached(&m->full_c, seenFC, nG + 1) && reached(&m->full_b, seenFB, nG + 1)) {
-            tc_fence_after();
+      const uint32_t tS = tb + 128 + 192 * h, tP = tS + 64, tY = tS + 128;
+      const uint32_t sHh = sH + h * (N * 128), sXdh = sXd + h * kBlk;
+      bool ok = true;
+      auto issue_yo = [&](uint32_t k) {   // Y <- C . H
+        ok = ok && wait2(&m->full_c, k & 1, m, STATUS_WAIT_TIMEOUT_TMA, status) &&
+             wait2(&m->bar_h[h], k & 1, m, STATUS_WAIT_TIMEOUT_SYNC, status);
+        if (ok && k > 0) ok = wait2(&m->bar_e[h], (k - 1) & 1, m, STATUS_WAIT_TIMEOUT_SYNC, status);
+        if (!ok) return;
+        tc_fence_after();
 #pragma unroll
-            for (int k = 0; k < KN; ++k) {
-              const uint32_t off = (k >> 2) * kBlk + (k & 3) * 32;
-              umma_ss(tG, umma_desc(dK, sC + off), umma_desc(dK, sB + off), idG, k > 0);
-            }
-            umma_commit(&m->bar_g);
-            ++nG;
-            progress = true;
-          }
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const uint32_t tY = tb + 128 + 192 * h + 128;
-            // Yo(k): state copy in place, previous Y tile read out, C landed
-            if (nYo[h] < ttot && reached(&m->full_c, seenFC, nYo[h] + 1) && reached(&m->bar_h[h], seenH[h], nYo[h] + 1) &&
-                reached(&m->bar_e[h], seenE[h], nYo[h])) {
-              tc_fence_after();
-#pragma unroll
-              for (int k = 0; k < KN; ++k) {
-                const uint32_t off = (k >> 2) * kBlk + (k & 3) * 32;
-                umma_ss(tY, umma_desc(dK, sC + off), umma_desc(dMN, sH + h * (N * 128) + k * 2048), idKM, k > 0);
-              }
-              umma_commit(&m->bar_yo[h]);
-              ++nYo[h];
-              progress = true;
-            }
-          }
+        for (int kk = 0; kk < KN; ++kk) {
+          const uint32_t off = (kk >> 2) * kBlk + (kk & 3) * 32;
+          umma_ss(tY, umma_desc(dK, sC + off), umma_desc(dMN, sHh + kk * 2048), idKM, kk > 0);
         }
+        umma_commit(&m->bar_yo[h]);
+        umma_commit(&m->empty_c);
+      };
+      auto issue_s = [&](uint32_t k) {    // S <- B^T . Xd
+        ok = ok && wait2(&m->full_b, k & 1, m, STATUS_WAIT_TIMEOUT_TMA, status) &&
+             wait2(&m->bar_xd[h], k & 1, m, STATUS_WAIT_TIMEOUT_SYNC, status);
+        if (!ok) return;
+        tc_fence_after();
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const uint32_t tS = tb + 128 + 192 * h;
-          if (nS[h] < ttot && reached(&m->full_b, seenFB, nS[h] + 1) && reached(&m->bar_xd[h], seenXd[h], nS[h] + 1)) {
-            tc_fence_after();
+        for (int kk = 0; kk < KT; ++kk)
+          umma_ss(tS, umma_desc(dMN, sB + kk * 2048), umma_desc(dMN, sXdh + kk * 2048), idMM, kk > 0);
+        umma_commit(&m->bar_s[h]);
+        umma_commit(&m->empty_b);
+      };
+      auto issue_yd = [&](uint32_t k) {   // Y += P . X
+        const uint32_t st = k % kXStages;
+        ok = ok && wait2(&m->bar_p[h], k & 1, m, STATUS_WAIT_TIMEOUT_SYNC, status) &&
+             wait2(&m->full_x[h][st], (k / kXStages) & 1, m, STATUS_WAIT_TIMEOUT_TMA, status);
+        if (!ok) return;
+        tc_fence_after();
 #pragma unroll
-            for (int k = 0; k < KT; ++k)
-              umma_ss(tS, umma_desc(dMN, sB + k * 2048), umma_desc(dMN, sXd + h * kBlk + k * 2048), idMM, k > 0);
-            umma_commit(&m->bar_s[h]);
-            if (!want_y) mbar_arrive(&m->empty_x[h][nS[h] & 1]);   // X was only read by the compute warps
-            ++nS[h];
-            progress = true;
-          }
+        for (int kk = 0; kk < KT; ++kk)
+          umma_ts(tY, tP + 8 * kk, umma_desc(dMN, sX + (kXStages * h + st) * kBlk + kk * 2048), idKM, 1);
+        umma_commit(&m->bar_y[h]);
+      };
+      // One uniform loop (a single copy of each task keeps the code small): per item,
+      //   j = 0..nt:  Yd(k0+j-1) if j > 0;  S(k0+j) if j < nt;  Yo(k0+j) if j < nt
+      // which is the order the head's warpgroup raises the barriers these tasks wait on.
+      uint32_t k0 = 0;   // running tile ordinal of the item's first tile
+      for (int item = blockIdx.x; item < prm.nitems && ok; item += gridDim.x) {
+        const int nt = decode_item(sp, prm.upairs, item).ntiles;
+#pragma unroll 1
+        for (int j = 0; j <= nt && ok; ++j) {
+          if (want_y && j > 0) issue_yd(k0 + j - 1);
+          if (j < nt) issue_s(k0 + j);
+          if (want_y && j < nt) issue_yo(k0 + j);
         }
-        if (want_y) {
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const uint32_t tP = tb + 128 + 192 * h + 64, tY = tb + 128 + 192 * h + 128;
-            const uint32_t k0 = nYd[h], st = k0 & 1;
-            if (k0 < ttot && reached(&m->bar_p[h], seenP[h], k0 + 1) &&
-                reached(&m->full_x[h][st], seenFX[h][st], (k0 >> 1) + 1)) {
-              tc_fence_after();
-#pragma unroll
-              for (int k = 0; k < KT; ++k)
-                umma_ts(tY, tP + 8 * k, umma_desc(dMN, sX + (2 * h + st) * kBlk + k * 2048), idKM, 1);
-              umma_commit(&m->bar_y[h]);
-              umma_commit(&m->empty_x[h][st]);
-              ++nYd[h];
-              progress = true;
-            }
-          }
-          const uint32_t cdone = min(nG, min(nYo[0], nYo[1]));
-          if (relC < cdone) { umma_commit(&m->empty_c); ++relC; progress = true; }
-        }
-        const uint32_t bdone = want_y ? min(nG, min(nS[0], nS[1])) : min(nS[0], nS[1]);
-        if (relB < bdone) { umma_commit(&m->empty_b); ++relB; progress = true; }
-        if (progress) {
-          last_progress = clock64();
-        } else {
-          if (m->abort_flag) break;
-          if (clock64() - last_progress > kWaitClocks) {
-            m->abort_flag = 1;
-            if (status) atomicCAS(status, 0, (int)STATUS_WAIT_TIMEOUT_SYNC);
-            break;
-          }
-        }
+        k0 += nt;
       }
     }
   } else {
     // ------------------------------------------------------------------ compute warpgroups (warps 4-7: head 0, 8-11: head 1)
-    setmaxnreg_inc<224>();
+    setmaxnreg_inc<216>();
     const int h = (warp - 4) >> 2;
     const int lane_base = (warp & 3) * 32;
     const int l = lane_base + lane;
@@ -308,35 +304,50 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       return __all_sync(0xffffffffu, wait2(bar, parity, m, code, status)) != 0;
     };
 
+#ifdef SSD_TC2_PROFILE
+    long long prof[24] = {};
+    long long pt = clock64();
+#define PROF(i) { const long long pn = clock64(); prof[i] += pn - pt; pt = pn; }
+#else
+#define PROF(i)
+#endif
     float H[P];
     float cs = 0.f, tot = 0.f, cs2 = 0.f;   // of the tile whose P / Y is being produced
-    double asum = 0.0;
+    float asum = 0.f, acomp = 0.f;   // compensated (Kahan) sum of the tile totals; FP64 is slow on this part
 
     // prefix sum of the log-decay over the 128 rows (model_ref.py:135); publishes cs*log2(e) for the P step
-    auto scan_tile = [&](float a, uint32_t par, float& cs_o, float& tot_o, float& cs2_o) {
+    auto scan_tile = [&](float a, float& cs_o, float& tot_o, float& cs2_o) {
       float v = a;
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {
         const float t = __shfl_up_sync(0xffffffffu, v, d);
         if (lane >= d) v += t;
       }
-      if (lane == 31) m->wsum[h][par][q] = v;
+      if (lane == 31) m->wsum[h][q] = v;
+      PROF(11)
       named_bar_sync(bar_id, 128);
-      const float w0 = m->wsum[h][par][0], w1 = m->wsum[h][par][1], w2 = m->wsum[h][par][2], w3 = m->wsum[h][par][3];
+      PROF(12)
+      const float w0 = m->wsum[h][0], w1 = m->wsum[h][1], w2 = m->wsum[h][2], w3 = m->wsum[h][3];
       cs_o = v + ((q > 0 ? w0 : 0.f) + (q > 1 ? w1 : 0.f) + (q > 2 ? w2 : 0.f));
       tot_o = (w0 + w1 + w2) + w3;
       cs2_o = cs_o * kLog2e;
-      m->cs2[h][par][l] = cs2_o;
+      m->cs2[h][l] = cs2_o;
+      // column factor of the factored decay mask: exp(cs at the end of this row's 32-token block - cs_row)
+      m->cf[h][l] = ex2(__shfl_sync(0xffffffffu, cs2_o, 31) - cs2_o);
       named_bar_sync(bar_id, 128);
+      PROF(13)
     };
     // Xd = exp(cs_last - cs_l) * x~ (model_ref.py:144,148) from X stage `st` into this head's Xd buffer
     auto make_xd = [&](uint32_t st, float cs_t, float tot_t, float dtv, bool has_dt) {
       const float dl = ex2((tot_t - cs_t) * kLog2e);
-      const uint32_t xrow = sX + (2 * h + st) * kBlk + l * 128, xdrow = sXdh + l * 128;
+      const uint32_t xrow = sX + (kXStages * h + st) * kBlk + l * 128, xdrow = sXdh + l * 128;
+      uint4 rawv[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) rawv[c] = lds128(xrow + ((c ^ swz) << 4));   // all loads first: their latencies overlap
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         const uint32_t phys = (c ^ swz) << 4;
-        uint4 raw = lds128(xrow + phys);
+        uint4 raw = rawv[c];
         float2 f0 = unpack2<T16>(raw.x), f1 = unpack2<T16>(raw.y), f2 = unpack2<T16>(raw.z), f3 = unpack2<T16>(raw.w);
         if (has_dt) {
           f0.x *= dtv; f0.y *= dtv; f1.x *= dtv; f1.y *= dtv; f2.x *= dtv; f2.y *= dtv; f3.x *= dtv; f3.y *= dtv;
@@ -384,149 +395,215 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 #pragma unroll
         for (int j = 0; j < P; ++j) H[j] = 0.f;
       }
-      asum = 0.0;
-      if (want_y) {
-        // the previous item's last C.H may still be reading this buffer
-        if (it > 0) { ok = cwait(&m->bar_yo[h], (it - 1) & 1, STATUS_WAIT_TIMEOUT_MMA); if (!ok) break; }
-        store_hb();
-        fence_proxy_async();
-        mbar_arrive(&m->bar_h[h]);
-      }
-      // ---- first tile of the item: prefix sum and Xd
+      asum = 0.f;
+      acomp = 0.f;
       float a_next = Ag[(int64_t)(w.t_begin + l) * sp.as[1]];
       float dt_next = Dg ? Cvt<T16>::to_f(Dg[(int64_t)(w.t_begin + l) * sp.dts[1]]) : 1.f;
-      {
-        const float a = a_next, dtv = dt_next;
-        if (w.ntiles > 1) {
-          a_next = Ag[(int64_t)(w.t_begin + T + l) * sp.as[1]];
-          if (Dg) dt_next = Cvt<T16>::to_f(Dg[(int64_t)(w.t_begin + T + l) * sp.dts[1]]);
-        }
-        // the previous S MMA of this head must be done with the Xd buffer
-        if (it > 0) { ok = cwait(&m->bar_s[h], (it - 1) & 1, STATUS_WAIT_TIMEOUT_MMA); if (!ok) break; }
-        scan_tile(a, it & 1, cs, tot, cs2);
-        ok = cwait(&m->full_x[h][it & 1], (it >> 1) & 1, STATUS_WAIT_TIMEOUT_TMA);
-        if (!ok) break;
-        make_xd(it & 1, cs, tot, dtv, Dg != nullptr);
-        fence_proxy_async();
-        mbar_arrive(&m->bar_xd[h]);
-      }
 
-      for (int j = 0; j < w.ntiles && ok; ++j, ++it) {
+      // Iteration j = -1 only prepares tile 0 (state copy, prefix sum, Xd); iteration j >= 0 finishes
+      // tile j (steps a, b, d, e) and prepares tile j + 1 (step c) in between, so that the S MMA of the
+      // next tile runs under steps d and e.  One copy of each step keeps the loop inside the
+      // instruction cache.
+#pragma unroll 1
+      for (int j = -1; j < w.ntiles && ok; ++j) {
         const int t0 = w.t_begin + j * T;
-        const bool last = (j + 1 == w.ntiles);
-        // ---- a. state: H <- exp(cs_last) H + S
-        ok = cwait(&m->bar_s[h], it & 1, STATUS_WAIT_TIMEOUT_MMA);
-        if (!ok) break;
-        tc_fence_after();
-        asum += (double)tot;
-        if (owns_state) {
-          const float g = ex2(tot * kLog2e);
-#pragma unroll
-          for (int hf = 0; hf < 2; ++hf) {
-            uint32_t sv[32];
-            tmem_ld32(tS + tlane + 32 * hf, sv);
-            tmem_ld_wait();
-#pragma unroll
-            for (int e = 0; e < 32; ++e) H[32 * hf + e] = fmaf(H[32 * hf + e], g, __uint_as_float(sv[e]));
-          }
-        }
-        if (want_y) {
-          // ---- b. Y <- exp(cs_l) * (C.H) in place; the MMA of step d accumulates P.X on top
-          ok = cwait(&m->bar_yo[h], it & 1, STATUS_WAIT_TIMEOUT_MMA);
+        const bool have_next = (j + 1 < w.ntiles);
+        if (j >= 0) {
+          // ---- a. state: H <- exp(cs_last) H + S
+        PROF(22)
+          ok = cwait(&m->bar_s[h], it & 1, STATUS_WAIT_TIMEOUT_MMA);
           if (!ok) break;
+        PROF(0)
           tc_fence_after();
-          const float el = ex2(cs2);
-#pragma unroll
-          for (int hf = 0; hf < 2; ++hf) {
-            uint32_t yv[32];
-            tmem_ld32(tY + tlane + 32 * hf, yv);
-            tmem_ld_wait();
-#pragma unroll
-            for (int e = 0; e < 32; ++e) yv[e] = __float_as_uint(__uint_as_float(yv[e]) * el);
-            tmem_st32(tY + tlane + 32 * hf, yv);
+          {
+            const float yk = tot - acomp, tk = asum + yk;
+            acomp = (tk - asum) - yk;
+            asum = tk;
           }
-          tmem_st_wait();
-          if (!last) {
-            store_hb();
-            fence_proxy_async();
-            mbar_arrive(&m->bar_h[h]);
+          if (owns_state) {
+            const float g = ex2(tot * kLog2e);
+            uint32_t sv0[32], sv1[32];
+            tmem_ld32(tS + tlane, sv0);
+            tmem_ld32(tS + tlane + 32, sv1);
+            tmem_ld_wait();
+        PROF(1)
+#pragma unroll
+            for (int e = 0; e < 32; ++e) H[e] = fmaf(H[e], g, __uint_as_float(sv0[e]));
+#pragma unroll
+            for (int e = 0; e < 32; ++e) H[32 + e] = fmaf(H[32 + e], g, __uint_as_float(sv1[e]));
+          }
+        PROF(2)
+          if (want_y) {
+            // ---- b. Y <- exp(cs_l) * (C.H) in place; the MMA of step d accumulates P.X on top
+            ok = cwait(&m->bar_yo[h], it & 1, STATUS_WAIT_TIMEOUT_MMA);
+            if (!ok) break;
+        PROF(3)
+            tc_fence_after();
+            const float el = ex2(cs2);
+            {
+              uint32_t y0[32], y1[32];
+              tmem_ld32(tY + tlane, y0);
+              tmem_ld32(tY + tlane + 32, y1);
+              tmem_ld_wait();
+        PROF(4)
+#pragma unroll
+              for (int e = 0; e < 32; ++e) y0[e] = __float_as_uint(__uint_as_float(y0[e]) * el);
+              tmem_st32(tY + tlane, y0);
+#pragma unroll
+              for (int e = 0; e < 32; ++e) y1[e] = __float_as_uint(__uint_as_float(y1[e]) * el);
+              tmem_st32(tY + tlane + 32, y1);
+            }
+        PROF(5)
+            tmem_st_wait();
+        PROF(6)
           }
         }
-        // ---- c. next tile: prefix sum and Xd (its S MMA then overlaps steps d and e)
+        // (all C.H MMAs that read the state copy have been waited for: the previous item's in its step b)
+        if (want_y && have_next) {
+          store_hb();
+          fence_proxy_async();
+          mbar_arrive(&m->bar_h[h]);
+        }
+        PROF(7)
+        if (j >= 0) {
+          if (want_y) {
+            // ---- d. P = (C B^T) o exp(segsum), causal -> TMEM (A operand, 16-bit pairs)
+            ok = cwait(&m->bar_g, it & 1, STATUS_WAIT_TIMEOUT_MMA);
+            if (!ok) break;
+        PROF(8)
+            tc_fence_after();
+            // Decay mask per 32-token column block J (rolled loop: one copy of each case):
+            //   J == q (diagonal block): exp2(cs_l - cs_s), causal, one ex2 per element;
+            //   J <  q: exp(cs_l - cs_s) = rf_J[l] * cf[s] with both factors <= 1 for non-positive
+            //           log-decays (rf_J[l] = exp(cs_l - cs_end(J)), cf[s] = exp(cs_end(J) - cs_s)): two multiplies;
+            //   J >  q: zero, written once (nothing else ever writes those TMEM columns).
+#pragma unroll 1
+            for (int J = 0; J < 4; ++J) {
+              uint32_t pk[16];
+              if (J > q) {
+                if (it != 0) continue;
+#pragma unroll
+                for (int e = 0; e < 16; ++e) pk[e] = 0u;
+              } else {
+                uint32_t gv[32];
+                tmem_ld32(tG + tlane + 32 * J, gv);
+                const bool diag = (J == q);
+                const float4* fv = reinterpret_cast<const float4*>(diag ? &m->cs2[h][32 * J] : &m->cf[h][32 * J]);
+                const float rf = diag ? 0.f : ex2(cs2 - m->cs2[h][32 * J + 31]);
+                float4 fq[8];
+#pragma unroll
+                for (int e4 = 0; e4 < 8; ++e4) fq[e4] = fv[e4];   // shared-memory latency overlaps the TMEM load
+                tmem_ld_wait();
+#pragma unroll
+                for (int e4 = 0; e4 < 8; ++e4) {
+                  const float4 c4 = fq[e4];
+                  const float cc[4] = {c4.x, c4.y, c4.z, c4.w};
+                  float pv[4];
+#pragma unroll
+                  for (int r = 0; r < 4; ++r) {
+                    const int e = 4 * e4 + r;
+                    const float gval = __uint_as_float(gv[e]);
+                    if (diag) {
+                      const float val = gval * ex2(cs2 - cc[r]);
+                      pv[r] = (32 * J + e <= l) ? val : 0.f;
+                    } else {
+                      pv[r] = gval * (rf * cc[r]);
+                    }
+                  }
+                  pk[2 * e4] = pack2<T16>(pv[0], pv[1]);
+                  pk[2 * e4 + 1] = pack2<T16>(pv[2], pv[3]);
+                }
+              }
+              tmem_st16(tP + tlane + 16 * J, pk);
+            }
+        PROF(9)
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(&m->bar_p[h]);
+        PROF(10)
+          }
+        }
+        // ---- c. next tile: prefix sum and Xd (the S MMA that read the Xd buffer was waited for in step a)
         float cs_n = 0.f, tot_n = 0.f, cs2_n = 0.f;
-        if (!last) {
+        if (have_next) {
+          const uint32_t itn = (j >= 0) ? it + 1 : it;
           const float a = a_next, dtv = dt_next;
           if (j + 2 < w.ntiles) {
             a_next = Ag[(int64_t)(t0 + 2 * T + l) * sp.as[1]];
             if (Dg) dt_next = Cvt<T16>::to_f(Dg[(int64_t)(t0 + 2 * T + l) * sp.dts[1]]);
           }
-          scan_tile(a, (it + 1) & 1, cs_n, tot_n, cs2_n);
-          ok = cwait(&m->full_x[h][(it + 1) & 1], ((it + 1) >> 1) & 1, STATUS_WAIT_TIMEOUT_TMA);
+          scan_tile(a, cs_n, tot_n, cs2_n);
+          ok = cwait(&m->full_x[h][itn % kXStages], (itn / kXStages) & 1, STATUS_WAIT_TIMEOUT_TMA);
           if (!ok) break;
-          make_xd((it + 1) & 1, cs_n, tot_n, dtv, Dg != nullptr);
+        PROF(14)
+          make_xd(itn % kXStages, cs_n, tot_n, dtv, Dg != nullptr);
+        PROF(15)
           fence_proxy_async();
           mbar_arrive(&m->bar_xd[h]);
+          if (!want_y) mbar_arrive(&m->empty_x[h][itn % kXStages]);   // nothing else reads X in state-only mode
         }
-        if (want_y) {
-          // ---- d. P = (C B^T) o exp(segsum), causal -> TMEM (A operand, 16-bit pairs)
-          ok = cwait(&m->bar_g, it & 1, STATUS_WAIT_TIMEOUT_MMA);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t par = it & 1;
-#pragma unroll
-          for (int jc = 0; jc < 4; ++jc) {
-            uint32_t pk[16];
-            if (jc > q) {
-#pragma unroll
-              for (int e = 0; e < 16; ++e) pk[e] = 0u;
-            } else {
-              uint32_t gv[32];
-              tmem_ld32(tG + tlane + 32 * jc, gv);
+        PROF(16)
+        if (j >= 0) {
+          if (want_y) {
+            // ---- e. Y -> global
+            ok = cwait(&m->bar_y[h], it & 1, STATUS_WAIT_TIMEOUT_MMA);
+            if (!ok) break;
+        PROF(17)
+            tc_fence_after();
+            // The X stage of this tile is dead (its P.X MMA is complete): stage the 16-bit Y rows there,
+            // then each warp copies its own 32 rows out with full 128-byte lines per 8 lanes.
+            const uint32_t xst = it % kXStages;
+            const uint32_t ystage = sX + (kXStages * h + xst) * kBlk;
+            {
+              uint32_t y0[32], y1[32];
+              tmem_ld32(tY + tlane, y0);
+              tmem_ld32(tY + tlane + 32, y1);
               tmem_ld_wait();
-              const float4* csv = reinterpret_cast<const float4*>(&m->cs2[h][par][32 * jc]);
+        PROF(18)
 #pragma unroll
-              for (int e4 = 0; e4 < 8; ++e4) {
-                const float4 c4 = csv[e4];
-                const float cc[4] = {c4.x, c4.y, c4.z, c4.w};
-                float pv[4];
+              for (int c = 0; c < 4; ++c) {
+                uint4 o;
+                o.x = pack2<T16>(__uint_as_float(y0[8 * c + 0]), __uint_as_float(y0[8 * c + 1]));
+                o.y = pack2<T16>(__uint_as_float(y0[8 * c + 2]), __uint_as_float(y0[8 * c + 3]));
+                o.z = pack2<T16>(__uint_as_float(y0[8 * c + 4]), __uint_as_float(y0[8 * c + 5]));
+                o.w = pack2<T16>(__uint_as_float(y0[8 * c + 6]), __uint_as_float(y0[8 * c + 7]));
+                sts128(ystage + l * 128 + ((c ^ swz) << 4), o);
+              }
 #pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                  const int e = 4 * e4 + r;
-                  const float val = __uint_as_float(gv[e]) * ex2(cs2 - cc[r]);
-                  pv[r] = (jc < q || 32 * jc + e <= l) ? val : 0.f;
-                }
-                pk[2 * e4] = pack2<T16>(pv[0], pv[1]);
-                pk[2 * e4 + 1] = pack2<T16>(pv[2], pv[3]);
+              for (int c = 0; c < 4; ++c) {
+                uint4 o;
+                o.x = pack2<T16>(__uint_as_float(y1[8 * c + 0]), __uint_as_float(y1[8 * c + 1]));
+                o.y = pack2<T16>(__uint_as_float(y1[8 * c + 2]), __uint_as_float(y1[8 * c + 3]));
+                o.z = pack2<T16>(__uint_as_float(y1[8 * c + 4]), __uint_as_float(y1[8 * c + 5]));
+                o.w = pack2<T16>(__uint_as_float(y1[8 * c + 6]), __uint_as_float(y1[8 * c + 7]));
+                sts128(ystage + l * 128 + (((4 + c) ^ swz) << 4), o);
               }
             }
-            tmem_st16(tP + tlane + 16 * jc, pk);
-          }
-          tmem_st_wait();
-          tc_fence_before();
-          mbar_arrive(&m->bar_p[h]);
-
-          // ---- e. Y -> global
-          ok = cwait(&m->bar_y[h], it & 1, STATUS_WAIT_TIMEOUT_MMA);
-          if (!ok) break;
-          tc_fence_after();
-          T16* yrow = Yg + (int64_t)(t0 + l) * sp.ys[1];
+        PROF(19)
+            __syncwarp();
+            {
+              const int cc = lane & 7;
+              T16* ybase = Yg + (int64_t)t0 * sp.ys[1] + cc * 8;
+              uint4 yv[8];
 #pragma unroll
-          for (int hf = 0; hf < 2; ++hf) {
-            uint32_t yv[32];
-            tmem_ld32(tY + tlane + 32 * hf, yv);
-            tmem_ld_wait();
+              for (int kq = 0; kq < 8; ++kq) {
+                const int r = lane_base + 4 * kq + (lane >> 3);
+                yv[kq] = lds128(ystage + r * 128 + ((cc ^ (r & 7)) << 4));
+              }
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              uint4 o;
-              o.x = pack2<T16>(__uint_as_float(yv[8 * c + 0]), __uint_as_float(yv[8 * c + 1]));
-              o.y = pack2<T16>(__uint_as_float(yv[8 * c + 2]), __uint_as_float(yv[8 * c + 3]));
-              o.z = pack2<T16>(__uint_as_float(yv[8 * c + 4]), __uint_as_float(yv[8 * c + 5]));
-              o.w = pack2<T16>(__uint_as_float(yv[8 * c + 6]), __uint_as_float(yv[8 * c + 7]));
-              *reinterpret_cast<uint4*>(yrow + 32 * hf + 8 * c) = o;
+              for (int kq = 0; kq < 8; ++kq) {
+                const int r = lane_base + 4 * kq + (lane >> 3);
+                *reinterpret_cast<uint4*>(ybase + (int64_t)r * sp.ys[1]) = yv[kq];
+              }
             }
+        PROF(20)
+            fence_proxy_async();   // generic writes to the stage are ordered before the TMA refill
+            mbar_arrive(&m->empty_x[h][xst]);
+            tc_fence_before();
+            mbar_arrive(&m->bar_e[h]);
+        PROF(21)
           }
-          tc_fence_before();
-          mbar_arrive(&m->bar_e[h]);
+          ++it;
         }
         cs = cs_n; tot = tot_n; cs2 = cs2_n;
       }
@@ -539,8 +616,13 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 #pragma unroll
         for (int j = 0; j < P / 4; ++j) F[j] = make_float4(H[4 * j], H[4 * j + 1], H[4 * j + 2], H[4 * j + 3]);
       }
-      if (sp.fin_ld && l == 0) sp.fin_ld[unit * sp.finld_unit_stride + w.seg * sp.finld_seg_stride] = (float)asum;
+      if (sp.fin_ld && l == 0) sp.fin_ld[unit * sp.finld_unit_stride + w.seg * sp.finld_seg_stride] = asum;
     }
+#ifdef SSD_TC2_PROFILE
+    if (blockIdx.x == 0 && h == 0 && (l == 0 || l == 96) && status) {
+      for (int i = 0; i < 24; ++i) status[2 + 24 * (l / 96) + i] = (int)(prof[i] >> 4);   // cycles / 16
+    }
+#endif
   }
 
   // ---------------------------------------------------------------------- teardown

@@ -25,7 +25,7 @@ def _status_word(device) -> torch.Tensor:
     key = (device.type, device.index)
     st = _status.get(key)
     if st is None:
-        st = torch.zeros(1, dtype=torch.int32, device=device)
+        st = torch.zeros(128, dtype=torch.int32, device=device)
         _status[key] = st
     return st
 
@@ -36,7 +36,7 @@ def device_status(device="cuda:0", clear: bool = True) -> int:
     device = torch.device(device)
     st = _status_word(device)
     torch.cuda.synchronize(device)
-    v = int(st.item())
+    v = int(st[0].item())
     if clear and v:
         st.zero_()
     return v
