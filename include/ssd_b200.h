@@ -108,6 +108,12 @@ size_t ssd_b200_workspace_bytes(const SsdArgs* args);
  * ("scan_f32", "tcgen05") or "invalid". */
 const char* ssd_b200_kernel_name(const SsdArgs* args);
 
+/* How ssd_b200_forward() will run these arguments: the resolved SSD_KERNEL_* family, the number of
+ * segments each sequence is cut into, and the number of kernel launches it enqueues (1; 3 for the
+ * two-pass segmented scan; 1 plus a memset for chained segments).  Any out pointer may be NULL.
+ * Returns SSD_OK or the validation error.  No reference counterpart. */
+int ssd_b200_plan(const SsdArgs* args, int32_t* kernel, int32_t* nsegments, int32_t* launches);
+
 /* The SSD forward: replaces SSDLayer._ssd_core, model_ref.py:123-162
  * (in-chunk prefix sum :135, decay mask :139-141, C.B^T :143, Y_diag :145,
  * chunk states :148-150, inter-chunk recurrence :152-157, Y_off :160-161,

@@ -22,6 +22,14 @@ def _ssd():
     return W
 
 
+@pytest.fixture(autouse=True)
+def _no_device_side_timeouts():
+    """Every kernel wait is bounded; a wait that ran out leaves a code in the status word."""
+    yield
+    if torch.cuda.is_available():
+        assert _ssd().device_status(DEV) == 0
+
+
 def _kernels_for(dtype, p, n):
     ks = ["scan_f32"]
     if dtype in (torch.float16, torch.bfloat16) and p == 64 and n in (64, 128):
@@ -199,6 +207,34 @@ def test_segmented_scan_equals_unsegmented(dtype):
         assert O.error_metrics(Y4.cpu(), Y1.cpu())[0] < TOL[dtype]
         Y3, _ = _run_and_check(inp, 128, kernel=kernel, nsegments=3)   # last segment shorter
         assert O.error_metrics(Y3.cpu(), Y1.cpu())[0] < TOL[dtype]
+
+
+def test_chained_segments_tensor_core():
+    """Enough (batch, head-pair) units to fill the SMs: the segments of a sequence are chained inside one
+    launch (state handed over through scratch) instead of scanned twice."""
+    if not _tc_available():
+        pytest.skip("tensor-core kernel not available")
+    W = _ssd()
+    inp = O.make_inputs(b=30, s=1024, h=8, p=64, n=128, g=2, dtype=torch.bfloat16, init=True, seed=21,
+                        decay_scale=0.02)
+    d = _to_dev(inp)
+    assert W.plan(d["X"], d["A"], d["B"], d["C"], 256, nsegments=4)["launches"] == 1
+    Y1, H1 = _run_and_check(inp, 256, kernel="tcgen05", nsegments=1)
+    Y4, H4 = _run_and_check(inp, 256, kernel="tcgen05", nsegments=4)
+    assert O.error_metrics(Y4.cpu(), Y1.cpu())[0] < 2e-2
+    H, D = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], 256, state_only=True, return_logdecay=True,
+                         kernel="tcgen05", nsegments=2, initial_states=d["initial_states"])
+    assert ((H - H1).abs().max() / H1.abs().max()) < 1e-3
+    assert torch.allclose(D.cpu().double(), O.total_logdecay(inp["A"]), rtol=1e-5, atol=1e-5)
+
+
+def test_one_head_per_cta_variant_when_groups_are_single_heads():
+    """Heads that do not pair up inside a B/C group (one head per group) take the single-head kernel."""
+    if not _tc_available():
+        pytest.skip("tensor-core kernel not available")
+    inp = O.make_inputs(b=2, s=512, h=3, p=64, n=128, g=3, dtype=torch.float16, init=True, seed=22, decay_scale=0.05)
+    _run_and_check(inp, 128, kernel="tcgen05")
+    _run_and_check(inp, 128, kernel="tcgen05", nsegments=2)
 
 
 def test_state_only_and_logdecay_outputs():

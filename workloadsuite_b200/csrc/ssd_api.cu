@@ -130,6 +130,24 @@ const char* ssd_b200_kernel_name(const SsdArgs* args) {
   return resolve_kernel(args) == SSD_KERNEL_TCGEN05 ? "tcgen05" : "scan_f32";
 }
 
+int ssd_b200_plan(const SsdArgs* args, int32_t* kernel_out, int32_t* nsegments_out, int32_t* launches_out) {
+  const int rc = validate(args);
+  if (rc != SSD_OK) return rc;
+  const int kernel = resolve_kernel(args);
+  int nseg, seg_len;
+  resolve_segments(args, kernel, &nseg, &seg_len);
+  const bool state_only = (args->flags & SSD_FLAG_STATE_ONLY) != 0;
+  int launches = 1;
+  if (nseg > 1) {
+    const bool chained = kernel == SSD_KERNEL_TCGEN05 && use_tc2(args) && ssd::tc2_chain_segments(*args, nseg);
+    launches = chained ? 1 : (state_only ? 2 : 3);
+  }
+  if (kernel_out) *kernel_out = kernel;
+  if (nsegments_out) *nsegments_out = nseg;
+  if (launches_out) *launches_out = launches;
+  return SSD_OK;
+}
+
 size_t ssd_b200_workspace_bytes(const SsdArgs* args) {
   if (validate(args) != SSD_OK) return 0;
   const int kernel = resolve_kernel(args);
@@ -138,7 +156,8 @@ size_t ssd_b200_workspace_bytes(const SsdArgs* args) {
   if (nseg <= 1) return 0;
   const size_t units = (size_t)args->batch * args->nheads;
   const size_t np = (size_t)args->dstate * args->headdim;
-  return align_up(units * nseg * np * sizeof(float), 256) + align_up(units * nseg * sizeof(float), 256);
+  // segment states, segment log-decay sums, and (chained mode) one ready flag per segment
+  return align_up(units * nseg * np * sizeof(float), 256) + 2 * align_up(units * nseg * sizeof(float), 256);
 }
 
 int ssd_b200_forward(const SsdArgs* args, void* stream_v) {
@@ -180,6 +199,29 @@ int ssd_b200_forward(const SsdArgs* args, void* stream_v) {
   float* seg_states = static_cast<float*>(args->workspace);
   float* seg_ld = reinterpret_cast<float*>(static_cast<char*>(args->workspace) +
                                             align_up((size_t)units * nseg * np * sizeof(float), 256));
+
+  if (kernel == SSD_KERNEL_TCGEN05 && use_tc2(args) && ssd::tc2_chain_segments(*args, nseg)) {
+    // one launch: the segments of a sequence hand their state over through the workspace
+    int32_t* flags = reinterpret_cast<int32_t*>(reinterpret_cast<char*>(seg_ld) +
+                                                align_up((size_t)units * nseg * sizeof(float), 256));
+    if (cudaMemsetAsync(flags, 0, (size_t)units * nseg * sizeof(int32_t), stream) != cudaSuccess) return SSD_ERR_CUDA;
+    ssd::ScanParams pc = prm;
+    pc.compute_y = state_only ? 0 : 1;
+    pc.chain = 1;
+    pc.chain_state = seg_states;
+    pc.chain_ld = seg_ld;
+    pc.chain_flag = flags;
+    pc.init = args->initial_state;   // only read by the first segment
+    pc.init_unit_stride = np;
+    pc.init_seg_stride = 0;
+    pc.fin = args->final_state;      // only written by the last segment
+    pc.fin_unit_stride = np;
+    pc.fin_seg_stride = 0;
+    pc.fin_ld = args->final_logdecay;
+    pc.finld_unit_stride = 1;
+    pc.finld_seg_stride = 0;
+    return launch_kernel(kernel, args, pc, stream);
+  }
 
   // pass 1: every segment from a zero state, state and log-decay sum only
   ssd::ScanParams p1 = prm;

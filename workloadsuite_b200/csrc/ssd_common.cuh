@@ -17,7 +17,8 @@ enum : int {
   STATUS_WAIT_TIMEOUT_MMA = 2,   // a bounded wait for a tcgen05 commit ran out
   STATUS_WAIT_TIMEOUT_SYNC = 3,  // a bounded wait between warps of one CTA ran out
   STATUS_TMEM_ALLOC = 4,         // tensor memory could not be allocated
-  STATUS_BAD_SMEM_ALIGNMENT = 5  // dynamic shared memory did not start on a 1024-byte boundary
+  STATUS_BAD_SMEM_ALIGNMENT = 5, // dynamic shared memory did not start on a 1024-byte boundary
+  STATUS_WAIT_TIMEOUT_CHAIN = 6  // a bounded wait for the previous segment of a chained sequence ran out
 };
 
 // One launch of a scan over [seg_begin, seg_end) of every (batch, head) unit.
@@ -40,6 +41,12 @@ struct ScanParams {
   int seg_len, nseg;
   int compute_y;
   int vec_ok;          // all row starts 16-byte aligned
+  // Chained segments (two-head tensor-core kernel only): segment k of a unit starts from the state that
+  // segment k-1 of the same unit left in chain_state, once chain_flag says it is there.
+  int chain;
+  float* chain_state;     // [unit][nseg][n*p]
+  float* chain_ld;        // [unit][nseg] running sum of the log-decay up to the end of the segment
+  int32_t* chain_flag;    // [unit][nseg], zeroed before the launch
   int64_t xs[3], as[3], bs[3], cs[3], dts[3], ys[3];
 };
 
@@ -76,6 +83,7 @@ int launch_tc(const SsdArgs& a, const ScanParams& prm, cudaStream_t stream);
 // two-heads-per-CTA tcgen05 kernel (ssd_tc2.cu): needs an even number of heads per B/C group
 bool tc2_supports(const SsdArgs& a);
 int tc2_default_segments(const SsdArgs& a);
+bool tc2_chain_segments(const SsdArgs& a, int nseg);   // true: one chained pass; false: two passes + fold
 int launch_tc2(const SsdArgs& a, const ScanParams& prm, cudaStream_t stream);
 
 }  // namespace ssd

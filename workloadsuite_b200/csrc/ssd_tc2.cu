@@ -383,7 +383,39 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       T16* Yg = want_y ? static_cast<T16*>(sp.Y) + w.bi * sp.ys[0] + hi * sp.ys[2] : nullptr;
 
       // ---- state entering the item
-      if (sp.init && owns_state) {
+      float asum0 = 0.f;   // log-decay summed over the earlier segments of a chained sequence
+      if (sp.chain && w.seg > 0) {
+        // wait (bounded) for the previous segment of this unit, which another CTA may still be finishing
+        const int64_t slot = unit * sp.nseg + (w.seg - 1);
+        if (l == 0) {
+          const long long c0 = clock64();
+          while (true) {
+            int f;
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(f) : "l"(sp.chain_flag + slot) : "memory");
+            if (f != 0) break;
+            if (m->abort_flag) break;
+            if (clock64() - c0 > kWaitClocks) {
+              m->abort_flag = 1;
+              if (status) atomicCAS(status, 0, (int)STATUS_WAIT_TIMEOUT_CHAIN);
+              break;
+            }
+          }
+        }
+        named_bar_sync(bar_id, 128);
+        if (m->abort_flag) { ok = false; break; }
+        if (owns_state) {
+          const float4* I = reinterpret_cast<const float4*>(sp.chain_state + slot * (int64_t)(N * P) + (int64_t)l * P);
+#pragma unroll
+          for (int j = 0; j < P / 4; ++j) {
+            const float4 v = __ldcg(I + j);   // written by another SM: bypass L1
+            H[4 * j] = v.x; H[4 * j + 1] = v.y; H[4 * j + 2] = v.z; H[4 * j + 3] = v.w;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < P; ++j) H[j] = 0.f;
+        }
+        asum0 = __ldcg(sp.chain_ld + slot);
+      } else if (sp.init && owns_state) {
         const float4* I = reinterpret_cast<const float4*>(sp.init + unit * sp.init_unit_stride +
                                                           w.seg * sp.init_seg_stride + (int64_t)l * P);
 #pragma unroll
@@ -610,13 +642,33 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       if (!ok) break;
 
       // ---- state leaving the item
-      if (sp.fin && owns_state) {
-        float4* F = reinterpret_cast<float4*>(sp.fin + unit * sp.fin_unit_stride + w.seg * sp.fin_seg_stride +
-                                              (int64_t)l * P);
+      const bool hand_over = sp.chain && (w.seg + 1 < sp.nseg);
+      if (hand_over) {
+        const int64_t slot = unit * sp.nseg + w.seg;
+        if (owns_state) {
+          float4* F = reinterpret_cast<float4*>(sp.chain_state + slot * (int64_t)(N * P) + (int64_t)l * P);
 #pragma unroll
-        for (int j = 0; j < P / 4; ++j) F[j] = make_float4(H[4 * j], H[4 * j + 1], H[4 * j + 2], H[4 * j + 3]);
+          for (int j = 0; j < P / 4; ++j) F[j] = make_float4(H[4 * j], H[4 * j + 1], H[4 * j + 2], H[4 * j + 3]);
+        }
+        if (l == 0) sp.chain_ld[slot] = asum0 + asum;
+        __threadfence();
+        named_bar_sync(bar_id, 128);
+        if (l == 0) {
+          const int one = 1;
+          asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(sp.chain_flag + slot), "r"(one) : "memory");
+        }
+      } else {
+        // last (or only) segment of the sequence: the caller's outputs
+        const int fseg = sp.chain ? 0 : w.seg;
+        if (sp.fin && owns_state) {
+          float4* F = reinterpret_cast<float4*>(sp.fin + unit * sp.fin_unit_stride + fseg * sp.fin_seg_stride +
+                                                (int64_t)l * P);
+#pragma unroll
+          for (int j = 0; j < P / 4; ++j) F[j] = make_float4(H[4 * j], H[4 * j + 1], H[4 * j + 2], H[4 * j + 3]);
+        }
+        if (sp.fin_ld && l == 0)
+          sp.fin_ld[unit * sp.finld_unit_stride + fseg * sp.finld_seg_stride] = asum0 + asum;
       }
-      if (sp.fin_ld && l == 0) sp.fin_ld[unit * sp.finld_unit_stride + w.seg * sp.finld_seg_stride] = asum;
     }
 #ifdef SSD_TC2_PROFILE
     if (blockIdx.x == 0 && h == 0 && (l == 0 || l == 96) && status) {
@@ -654,10 +706,31 @@ bool tc2_supports(const SsdArgs& a) {
   return a.nheads % 2 == 0 && hpg % 2 == 0;
 }
 
+// Rounds of `items` equal work items over the persistent grid, as a fraction of the ideal.
+static double round_efficiency(int64_t items) {
+  const int64_t rounds = (items + kSms - 1) / kSms;
+  return (double)items / (double)(rounds * kSms);
+}
+
+// With at least about one item per SM the segments of a sequence are chained inside one launch (each
+// starts from the state its predecessor left in scratch): that only serves to even out the last round.
+// With fewer sequences than SMs the segments must run concurrently instead: two passes and a fold.
+bool tc2_chain_segments(const SsdArgs& a, int nseg) {
+  const int64_t upairs = (int64_t)a.batch * a.nheads / 2;
+  return nseg > 1 && upairs >= 120;
+}
+
 int tc2_default_segments(const SsdArgs& a) {
   const int64_t upairs = (int64_t)a.batch * a.nheads / 2;
-  if (upairs >= 100) return 1;
   const int tiles = a.seqlen / T;
+  if (upairs >= 120) {
+    int best = 1;
+    for (int nseg = 1; nseg <= 16 && tiles / nseg >= 4; nseg *= 2) {
+      best = nseg;
+      if (round_efficiency(upairs * nseg) >= 0.92) break;
+    }
+    return best;
+  }
   int want = (int)((2 * kSms + upairs - 1) / upairs);
   want = std::min(want, std::max(1, tiles / 4));
   return std::max(1, want);

@@ -198,18 +198,18 @@ def kernel_name(X, A, B, C_, chunk, kernel=None) -> str:
     return _lib.load().ssd_b200_kernel_name(C.byref(args)).decode()
 
 
-def plan(X, A, B, C_, chunk, kernel=None, nsegments=None) -> dict:
-    """Kernel family, scratch bytes and kernel launches ``ssd_forward`` uses for these tensors."""
+def plan(X, A, B, C_, chunk, kernel=None, nsegments=None, state_only=False) -> dict:
+    """Kernel family, segments per sequence, kernel launches and scratch bytes ``ssd_forward`` uses."""
     _check(X, A, B, C_, None, None)
     args = _lib.SsdArgs()
-    _fill(args, X, A, B, C_, None, None, None, None, None, chunk, kernel, nsegments, False)
+    _fill(args, X, A, B, C_, None, None, None, None, None, chunk, kernel, nsegments, state_only)
     lib = _lib.load()
-    ws = lib.ssd_b200_workspace_bytes(C.byref(args))
-    np_ = X.shape[3] * B.shape[3]
-    units = X.shape[0] * X.shape[2]
-    nseg = 1 if ws == 0 else max(2, round(ws / (units * (np_ + 1) * 4)))
-    return {"kernel": lib.ssd_b200_kernel_name(C.byref(args)).decode(), "workspace_bytes": int(ws),
-            "launches": 1 if ws == 0 else 3, "nsegments": nseg}
+    k, nseg, launches = C.c_int32(), C.c_int32(), C.c_int32()
+    rc = lib.ssd_b200_plan(C.byref(args), C.byref(k), C.byref(nseg), C.byref(launches))
+    if rc != _lib.SSD_OK:
+        _raise(rc)
+    return {"kernel": lib.ssd_b200_kernel_name(C.byref(args)).decode(), "nsegments": nseg.value,
+            "launches": launches.value, "workspace_bytes": int(lib.ssd_b200_workspace_bytes(C.byref(args)))}
 
 
 def fold_states(states: torch.Tensor, logdecays: torch.Tensor, rank: int,
