@@ -237,6 +237,24 @@ def test_one_head_per_cta_variant_when_groups_are_single_heads():
     _run_and_check(inp, 128, kernel="tcgen05", nsegments=2)
 
 
+def test_reuse_of_segment_states_after_a_state_only_run():
+    """The sequence-sharded forward runs state-only, exchanges states, then runs again seeded: the second
+    run may reuse the per-segment states of the first (two-pass segmented scan)."""
+    W = _ssd()
+    inp = O.make_inputs(b=1, s=2048, h=4, p=64, n=128, g=1, dtype=torch.bfloat16, init=True, seed=23,
+                        decay_scale=0.01)
+    d = _to_dev(inp)
+    for kernel in _kernels_for(torch.bfloat16, 64, 128):
+        if kernel == "tcgen05" and not _tc_available():
+            continue
+        want = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], 256, initial_states=d["initial_states"], kernel=kernel,
+                             nsegments=4)
+        W.ssd_forward(d["X"], d["A"], d["B"], d["C"], 256, state_only=True, kernel=kernel, nsegments=4)
+        got = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], 256, initial_states=d["initial_states"], kernel=kernel,
+                            nsegments=4, reuse_segments=True)
+        assert torch.equal(got, want)
+
+
 def test_state_only_and_logdecay_outputs():
     W = _ssd()
     inp = O.make_inputs(b=2, s=512, h=3, p=64, n=64, g=1, dtype=torch.bfloat16, seed=10, decay_scale=0.05)

@@ -141,6 +141,7 @@ int ssd_b200_plan(const SsdArgs* args, int32_t* kernel_out, int32_t* nsegments_o
   if (nseg > 1) {
     const bool chained = kernel == SSD_KERNEL_TCGEN05 && use_tc2(args) && ssd::tc2_chain_segments(*args, nseg);
     launches = chained ? 1 : (state_only ? 2 : 3);
+    if (!chained && (args->flags & SSD_FLAG_REUSE_SEGMENTS)) launches -= 1;
   }
   if (kernel_out) *kernel_out = kernel;
   if (nsegments_out) *nsegments_out = nseg;
@@ -156,8 +157,9 @@ size_t ssd_b200_workspace_bytes(const SsdArgs* args) {
   if (nseg <= 1) return 0;
   const size_t units = (size_t)args->batch * args->nheads;
   const size_t np = (size_t)args->dstate * args->headdim;
-  // segment states, segment log-decay sums, and (chained mode) one ready flag per segment
-  return align_up(units * nseg * np * sizeof(float), 256) + 2 * align_up(units * nseg * sizeof(float), 256);
+  // zero-start segment states, states entering the segments, segment log-decay sums, and (chained mode) one
+  // ready flag per segment
+  return 2 * align_up(units * nseg * np * sizeof(float), 256) + 2 * align_up(units * nseg * sizeof(float), 256);
 }
 
 int ssd_b200_forward(const SsdArgs* args, void* stream_v) {
@@ -197,8 +199,9 @@ int ssd_b200_forward(const SsdArgs* args, void* stream_v) {
   if (!args->workspace || args->workspace_bytes < need) return SSD_ERR_WORKSPACE;
   if (reinterpret_cast<uintptr_t>(args->workspace) & 255) return SSD_ERR_MISALIGNED;
   float* seg_states = static_cast<float*>(args->workspace);
-  float* seg_ld = reinterpret_cast<float*>(static_cast<char*>(args->workspace) +
-                                            align_up((size_t)units * nseg * np * sizeof(float), 256));
+  const size_t st_bytes = align_up((size_t)units * nseg * np * sizeof(float), 256);
+  float* seg_in = reinterpret_cast<float*>(static_cast<char*>(args->workspace) + st_bytes);
+  float* seg_ld = reinterpret_cast<float*>(static_cast<char*>(args->workspace) + 2 * st_bytes);
 
   if (kernel == SSD_KERNEL_TCGEN05 && use_tc2(args) && ssd::tc2_chain_segments(*args, nseg)) {
     // one launch: the segments of a sequence hand their state over through the workspace
@@ -224,28 +227,32 @@ int ssd_b200_forward(const SsdArgs* args, void* stream_v) {
   }
 
   // pass 1: every segment from a zero state, state and log-decay sum only
-  ssd::ScanParams p1 = prm;
-  p1.compute_y = 0;
-  p1.Y = nullptr;
-  p1.init = nullptr;
-  p1.fin = seg_states;
-  p1.fin_unit_stride = (int64_t)nseg * np;
-  p1.fin_seg_stride = np;
-  p1.fin_ld = seg_ld;
-  p1.finld_unit_stride = nseg;
-  p1.finld_seg_stride = 1;
-  rc = launch_kernel(kernel, args, p1, stream);
-  if (rc != SSD_OK) return rc;
+  if (!(args->flags & SSD_FLAG_REUSE_SEGMENTS)) {
+    ssd::ScanParams p1 = prm;
+    p1.compute_y = 0;
+    p1.Y = nullptr;
+    p1.init = nullptr;
+    p1.fin = seg_states;
+    p1.fin_unit_stride = (int64_t)nseg * np;
+    p1.fin_seg_stride = np;
+    p1.fin_ld = seg_ld;
+    p1.finld_unit_stride = nseg;
+    p1.finld_seg_stride = 1;
+    rc = launch_kernel(kernel, args, p1, stream);
+    if (rc != SSD_OK) return rc;
+  }
 
-  // fold: state entering each segment (in place), final state, total log-decay
+  // fold: state entering each segment (kept apart from the zero-start states, so that those can be
+  // reused), final state, total log-decay
   rc = ssd::launch_fold(seg_states, (int64_t)nseg * np, np, seg_ld, nseg, 1, args->initial_state, nullptr,
-                        args->final_state, args->final_logdecay, nseg, 1, units, np, stream);
+                        args->final_state, args->final_logdecay, nseg, state_only ? nullptr : seg_in, units, np,
+                        stream);
   if (rc != SSD_OK || state_only) return rc;
 
   // pass 2: every segment again, seeded with its incoming state, writing Y
   ssd::ScanParams p2 = prm;
   p2.compute_y = 1;
-  p2.init = seg_states;
+  p2.init = seg_in;
   p2.init_unit_stride = (int64_t)nseg * np;
   p2.init_seg_stride = np;
   p2.fin = nullptr;
@@ -258,8 +265,8 @@ int ssd_b200_fold_states(const float* states, int64_t states_shard_stride, const
                          int32_t rank, int64_t units, int64_t np, void* stream) {
   if (!states || !logdecay || !out) return SSD_ERR_NULL_POINTER;
   if (nshards <= 0 || rank < 0 || rank > nshards || units <= 0 || np <= 0) return SSD_ERR_BAD_SHAPE;
-  return ssd::launch_fold(const_cast<float*>(states), np, states_shard_stride, logdecay, 1, logdecay_shard_stride,
-                          initial, out, nullptr, nullptr, rank, 0, units, np, static_cast<cudaStream_t>(stream));
+  return ssd::launch_fold(states, np, states_shard_stride, logdecay, 1, logdecay_shard_stride, initial, out, nullptr,
+                          nullptr, rank, nullptr, units, np, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -70,9 +70,10 @@ int launch_scan_f32(const ScanParams& prm, int dtype, cudaStream_t stream);
 bool scan_f32_supports(int p, int n);
 int scan_f32_tile_tokens();
 
-int launch_fold(float* states, int64_t st_unit_stride, int64_t st_seg_stride, const float* ld,
+// `incoming` (nullable, may alias `states`) receives the state entering every segment, in the layout of `states`.
+int launch_fold(const float* states, int64_t st_unit_stride, int64_t st_seg_stride, const float* ld,
                 int64_t ld_unit_stride, int64_t ld_seg_stride, const float* init, float* out_single,
-                float* out_final, float* out_ld, int upto, int write_incoming_in_place, int64_t units, int64_t np,
+                float* out_final, float* out_ld, int upto, float* incoming, int64_t units, int64_t np,
                 cudaStream_t stream);
 
 // tcgen05 kernel family (ssd_tcgen05.cu)

@@ -240,18 +240,19 @@ __global__ void __launch_bounds__(kThreads) ssd_scan_f32_kernel(const ScanParams
 
 // H_in(seg) for every segment of every unit, from the zero-start final states:
 //   run = init; for seg: emit run; run = run * exp(D_seg) + F_seg.
-__global__ void ssd_fold_kernel(float* states, int64_t st_unit_stride, int64_t st_seg_stride, const float* ld,
+__global__ void ssd_fold_kernel(const float* states, int64_t st_unit_stride, int64_t st_seg_stride, const float* ld,
                                 int64_t ld_unit_stride, int64_t ld_seg_stride, const float* init, float* out_single,
-                                float* out_final, float* out_ld, int upto, int in_place, int64_t np) {
+                                float* out_final, float* out_ld, int upto, float* incoming, int64_t np) {
   const int64_t unit = blockIdx.x;
   const int64_t e = (int64_t)blockIdx.y * blockDim.x + threadIdx.x;
   if (e >= np) return;
   float run = init ? init[unit * np + e] : 0.f;
-  float* F = states + unit * st_unit_stride + e;
+  const float* F = states + unit * st_unit_stride + e;
+  float* G = incoming ? incoming + unit * st_unit_stride + e : nullptr;   // same layout as `states`
   const float* D = ld + unit * ld_unit_stride;
   for (int s = 0; s < upto; ++s) {
     const float f = F[(int64_t)s * st_seg_stride];
-    if (in_place) F[(int64_t)s * st_seg_stride] = run;
+    if (G) G[(int64_t)s * st_seg_stride] = run;
     run = fmaf(run, expf(D[(int64_t)s * ld_seg_stride]), f);
   }
   if (out_single) out_single[unit * np + e] = run;
@@ -315,16 +316,16 @@ int launch_scan_f32(const ScanParams& prm, int dtype, cudaStream_t stream) {
   }
 }
 
-int launch_fold(float* states, int64_t st_unit_stride, int64_t st_seg_stride, const float* ld,
+int launch_fold(const float* states, int64_t st_unit_stride, int64_t st_seg_stride, const float* ld,
                 int64_t ld_unit_stride, int64_t ld_seg_stride, const float* init, float* out_single,
-                float* out_final, float* out_ld, int upto, int write_incoming_in_place, int64_t units, int64_t np,
+                float* out_final, float* out_ld, int upto, float* incoming, int64_t units, int64_t np,
                 cudaStream_t stream) {
   if (units <= 0 || np <= 0) return SSD_ERR_BAD_SHAPE;
   if (units > 0x7fffffff || (np + 255) / 256 > 65535) return SSD_ERR_TOO_LARGE;
   dim3 grid((unsigned)units, (unsigned)((np + 255) / 256));
   ssd_fold_kernel<<<grid, 256, 0, stream>>>(states, st_unit_stride, st_seg_stride, ld, ld_unit_stride,
                                             ld_seg_stride, init, out_single, out_final, out_ld, upto,
-                                            write_incoming_in_place, np);
+                                            incoming, np);
   return cudaGetLastError() == cudaSuccess ? SSD_OK : SSD_ERR_CUDA;
 }
 

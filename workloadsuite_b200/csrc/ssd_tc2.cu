@@ -731,9 +731,21 @@ int tc2_default_segments(const SsdArgs& a) {
     }
     return best;
   }
-  int want = (int)((2 * kSms + upairs - 1) / upairs);
-  want = std::min(want, std::max(1, tiles / 4));
-  return std::max(1, want);
+  // Fewer sequences than SMs: cutting them into concurrently scanned segments costs a second pass
+  // (about 0.4 of a full pass) and a per-item start-up (about 1.5 tile times).  Pick the count that
+  // minimises the modelled time, in tile times, of the busiest CTA.
+  double best_cost = (double)((upairs + kSms - 1) / kSms) * (tiles + 1.5);
+  int best = 1;
+  for (int nseg = 2; nseg <= 32 && nseg * 2 <= tiles; ++nseg) {
+    const int64_t rounds = (upairs * nseg + kSms - 1) / kSms;
+    const int per_item = (tiles + nseg - 1) / nseg;
+    const double cost = (double)rounds * (per_item * 1.4 + 3.0);
+    if (cost < best_cost * 0.97) {
+      best_cost = cost;
+      best = nseg;
+    }
+  }
+  return best;
 }
 
 int launch_tc2(const SsdArgs& a, const ScanParams& sp, cudaStream_t stream) {

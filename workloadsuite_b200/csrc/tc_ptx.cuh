@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the SSD kernel uses:
-// mbarrier, TMA (cp.async.bulk.tensor, no multicast), tcgen05 MMA / TMEM.
+// mbarrier, TMA (plain per-CTA cp.async.bulk.tensor loads), tcgen05 MMA / TMEM.
 // Every wait is bounded: it returns false after a fixed number of polls.
 #pragma once
 

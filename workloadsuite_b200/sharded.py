@@ -58,7 +58,8 @@ def _cuda_scan(X, A, B, C, chunk, dt=None, initial_states=None, state_only=False
     if state_only:
         return ssd_forward(X, A, B, C, chunk, dt=dt, initial_states=initial_states, state_only=True,
                            return_logdecay=True, **kw)
-    return ssd_forward(X, A, B, C, chunk, dt=dt, initial_states=initial_states, **kw)
+    # the state-only call that precedes this one left its per-segment states in the workspace
+    return ssd_forward(X, A, B, C, chunk, dt=dt, initial_states=initial_states, reuse_segments=True, **kw)
 
 
 def _cuda_fold(states, logdecays, rank, initial=None):

@@ -89,7 +89,8 @@ def _check(X, A, B, Cm, dt, initial_states):
     return b, s, h, p, g, n
 
 
-def _fill(args, X, A, B, Cm, dt, initial_states, Y, final_state, final_ld, chunk, kernel, nsegments, state_only):
+def _fill(args, X, A, B, Cm, dt, initial_states, Y, final_state, final_ld, chunk, kernel, nsegments, state_only,
+          reuse_segments=False):
     b, s, h, p = X.shape
     args.X, args.A, args.B, args.C = X.data_ptr(), A.data_ptr(), B.data_ptr(), Cm.data_ptr()
     args.dt = dt.data_ptr() if dt is not None else None
@@ -105,7 +106,7 @@ def _fill(args, X, A, B, Cm, dt, initial_states, Y, final_state, final_ld, chunk
         raise ValueError(f"kernel must be one of {sorted(k for k in _KERNELS if k)}")
     args.kernel = _KERNELS[kernel]
     args.status = _status_word(X.device).data_ptr() if X.is_cuda else None
-    args.flags = _lib.FLAG_STATE_ONLY if state_only else 0
+    args.flags = (_lib.FLAG_STATE_ONLY if state_only else 0) | (_lib.FLAG_REUSE_SEGMENTS if reuse_segments else 0)
     args.nsegments = int(nsegments or 0)
     args.x_stride = _strides3(X, "X")
     args.a_stride = (C.c_int64 * 3)(*A.stride())
@@ -142,6 +143,7 @@ def ssd_forward(
     kernel: Optional[str] = None,
     nsegments: Optional[int] = None,
     out: Optional[torch.Tensor] = None,
+    reuse_segments: bool = False,
 ):
     """Mamba-2 SSD forward ``Y = SSD(X, A, B, C)`` on the current CUDA stream.
 
@@ -156,6 +158,8 @@ def ssd_forward(
 
     Returns Y [b,s,h,p] in X's dtype, plus the float32 final state [b,h,n,p] and/or
     the summed log-decay [b,h] when asked.  With ``state_only`` no Y is produced.
+    ``reuse_segments`` tells a segmented two-pass scan that the previous call on this device was the
+    ``state_only`` run over the same tensors, so its per-segment states need not be recomputed.
     """
     if not X.is_cuda:
         raise RuntimeError("ssd_forward needs CUDA tensors (there is no CPU path); see ssd_forward_host")
@@ -173,7 +177,8 @@ def ssd_forward(
     final_state = torch.empty((b, h, n, p), dtype=torch.float32, device=dev) if want_final else None
     final_ld = torch.empty((b, h), dtype=torch.float32, device=dev) if return_logdecay else None
     args = _lib.SsdArgs()
-    _fill(args, X, A, B, C_, dt, initial_states, Y, final_state, final_ld, chunk, kernel, nsegments, state_only)
+    _fill(args, X, A, B, C_, dt, initial_states, Y, final_state, final_ld, chunk, kernel, nsegments, state_only,
+          reuse_segments)
     with torch.cuda.device(dev):
         need = lib.ssd_b200_workspace_bytes(C.byref(args))
         ws = _workspace(dev, need)
