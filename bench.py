@@ -298,8 +298,14 @@ def main():
     kw = dict(kernel=args.kernel, nsegments=args.nsegments or None)
 
     plan = W.plan(sets[0]["X"], sets[0]["A"], sets[0]["B"], sets[0]["C"], chunk, **kw)
-    # sequence-parallel: state-only pass + fold + seeded pass (plus NCCL's own all-gather kernel)
-    launches_per_step = [2 * plan["launches"] + 1 if seq_parallel else plan["launches"]]
+    if seq_parallel:
+        # state-only run + cross-rank fold + seeded run that reuses the per-segment states (NCCL's own
+        # all-gather kernel and two small copies into the send buffer are not counted)
+        p_state = W.plan(sets[0]["X"], sets[0]["A"], sets[0]["B"], sets[0]["C"], chunk, state_only=True, **kw)
+        seeded = plan["launches"] - 1 if plan["nsegments"] > 1 and plan["launches"] == 3 else plan["launches"]
+        launches_per_step = [p_state["launches"] + 1 + seeded]
+    else:
+        launches_per_step = [plan["launches"]]
     if seq_parallel:
         eng = sharded.SequenceShardedSSD()
 

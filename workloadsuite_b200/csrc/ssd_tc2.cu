@@ -55,10 +55,9 @@ struct Misc2 {
   uint32_t tmem_base;
   volatile int abort_flag;
   float wsum[2][4];
-  // Single-buffered: they are rewritten in step c, behind a warpgroup barrier that every warp reaches only
-  // after its step d (the only reader) of the current tile.
-  alignas(16) float cs2[2][T];   // [head][row]: prefix sum of the log-decay times log2(e)
-  alignas(16) float cf[2][T];    // [head][row]: exp(cs of the row's 32-block end - cs of the row)
+  // Double-buffered by tile parity: step c writes the next tile's values while step d still reads this tile's.
+  alignas(16) float cf[2][2][T];   // [head][parity][row]: exp(cs at the end of the row's 32-block - cs of the row)
+  float cend[2][2][4];             // [head][parity][block]: cs * log2(e) at the end of each 32-row block
 };
 
 static_assert(sizeof(Misc2) <= 2560, "Misc2 outgrew its shared-memory slot");
@@ -105,7 +104,8 @@ __device__ __forceinline__ bool wait2(uint64_t* bar, uint32_t parity, Misc2* m, 
 template <typename T16, int N>
 __global__ void __launch_bounds__(kThreads2, 1)
 ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ CUtensorMap tmC, const Tc2Params prm) {
+               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmY,
+               const Tc2Params prm) {
   using L = Layout2<N>;
   constexpr int NB = L::NB;
   constexpr int KN = N / 16;
@@ -128,8 +128,12 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     mbar_init(&m->empty_b, want_y ? 3 : 2); mbar_init(&m->empty_c, 3);
     mbar_init(&m->bar_g, 1);
     for (int h = 0; h < 2; ++h) {
-      // an X stage is handed back by the 128 threads of the head's warpgroup (after they have used it to stage Y)
-      for (int s = 0; s < kXStages; ++s) { mbar_init(&m->full_x[h][s], 1); mbar_init(&m->empty_x[h][s], 128); }
+      // an X stage is handed back by the head's warpgroup once it is done with it (in Y mode: after the stage
+      // has served as the source of the TMA store of Y)
+      for (int s = 0; s < kXStages; ++s) {
+        mbar_init(&m->full_x[h][s], 1);
+        mbar_init(&m->empty_x[h][s], want_y ? 1 : 128);   // Y mode: the thread that issued the TMA store of Y
+      }
       mbar_init(&m->bar_yo[h], 1); mbar_init(&m->bar_s[h], 1); mbar_init(&m->bar_y[h], 1);
       mbar_init(&m->bar_xd[h], 128); mbar_init(&m->bar_h[h], 128); mbar_init(&m->bar_p[h], 128);
       mbar_init(&m->bar_e[h], 128);
@@ -150,7 +154,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     setmaxnreg_dec<72>();   // 128*72 + 256*216 = 384*168: the CTA can only re-divide its own allocation
     if (warp == 0 && lane == 0) {
       // ---------------------------------------------------------------- TMA producer
-      prefetch_tmap(&tmX); prefetch_tmap(&tmB); prefetch_tmap(&tmC);
+      prefetch_tmap(&tmX); prefetch_tmap(&tmB); prefetch_tmap(&tmC); prefetch_tmap(&tmY);
       bool ok = true;
       uint32_t it = 0;   // running tile ordinal of this CTA
       for (int item = blockIdx.x; item < prm.nitems && ok; item += gridDim.x) {
@@ -313,10 +317,12 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 #endif
     float H[P];
     float cs = 0.f, tot = 0.f, cs2 = 0.f;   // of the tile whose P / Y is being produced
+    bool store_pending = false;    // (thread l == 0) a TMA store of Y is in flight from X stage store_stage
+    uint32_t store_stage = 0;
     float asum = 0.f, acomp = 0.f;   // compensated (Kahan) sum of the tile totals; FP64 is slow on this part
 
     // prefix sum of the log-decay over the 128 rows (model_ref.py:135); publishes cs*log2(e) for the P step
-    auto scan_tile = [&](float a, float& cs_o, float& tot_o, float& cs2_o) {
+    auto scan_tile = [&](float a, uint32_t par, float& cs_o, float& tot_o, float& cs2_o) {
       float v = a;
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {
@@ -331,9 +337,9 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       cs_o = v + ((q > 0 ? w0 : 0.f) + (q > 1 ? w1 : 0.f) + (q > 2 ? w2 : 0.f));
       tot_o = (w0 + w1 + w2) + w3;
       cs2_o = cs_o * kLog2e;
-      m->cs2[h][l] = cs2_o;
       // column factor of the factored decay mask: exp(cs at the end of this row's 32-token block - cs_row)
-      m->cf[h][l] = ex2(__shfl_sync(0xffffffffu, cs2_o, 31) - cs2_o);
+      m->cf[h][par][l] = ex2(__shfl_sync(0xffffffffu, cs2_o, 31) - cs2_o);
+      if (lane == 31) m->cend[h][par][q] = cs2_o;
       named_bar_sync(bar_id, 128);
       PROF(13)
     };
@@ -341,6 +347,8 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     auto make_xd = [&](uint32_t st, float cs_t, float tot_t, float dtv, bool has_dt) {
       const float dl = ex2((tot_t - cs_t) * kLog2e);
       const uint32_t xrow = sX + (kXStages * h + st) * kBlk + l * 128, xdrow = sXdh + l * 128;
+      // packed 16-bit arithmetic, as the reference does for X*dt and the decay-scaled X (model_ref.py:144,148)
+      const uint32_t dl2 = pack2<T16>(dl, dl), dt2 = pack2<T16>(dtv, dtv);
       uint4 rawv[8];
 #pragma unroll
       for (int c = 0; c < 8; ++c) rawv[c] = lds128(xrow + ((c ^ swz) << 4));   // all loads first: their latencies overlap
@@ -348,16 +356,14 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       for (int c = 0; c < 8; ++c) {
         const uint32_t phys = (c ^ swz) << 4;
         uint4 raw = rawv[c];
-        float2 f0 = unpack2<T16>(raw.x), f1 = unpack2<T16>(raw.y), f2 = unpack2<T16>(raw.z), f3 = unpack2<T16>(raw.w);
         if (has_dt) {
-          f0.x *= dtv; f0.y *= dtv; f1.x *= dtv; f1.y *= dtv; f2.x *= dtv; f2.y *= dtv; f3.x *= dtv; f3.y *= dtv;
-          raw.x = pack2<T16>(f0.x, f0.y); raw.y = pack2<T16>(f1.x, f1.y);
-          raw.z = pack2<T16>(f2.x, f2.y); raw.w = pack2<T16>(f3.x, f3.y);
-          sts128(xrow + phys, raw);
+          raw.x = mul2<T16>(raw.x, dt2); raw.y = mul2<T16>(raw.y, dt2);
+          raw.z = mul2<T16>(raw.z, dt2); raw.w = mul2<T16>(raw.w, dt2);
+          sts128(xrow + phys, raw);   // x~ replaces x as the operand of P . X
         }
         uint4 o;
-        o.x = pack2<T16>(f0.x * dl, f0.y * dl); o.y = pack2<T16>(f1.x * dl, f1.y * dl);
-        o.z = pack2<T16>(f2.x * dl, f2.y * dl); o.w = pack2<T16>(f3.x * dl, f3.y * dl);
+        o.x = mul2<T16>(raw.x, dl2); o.y = mul2<T16>(raw.y, dl2);
+        o.z = mul2<T16>(raw.z, dl2); o.w = mul2<T16>(raw.w, dl2);
         sts128(xdrow + phys, o);
       }
     };
@@ -436,6 +442,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       // tile j (steps a, b, d, e) and prepares tile j + 1 (step c) in between, so that the S MMA of the
       // next tile runs under steps d and e.  One copy of each step keeps the loop inside the
       // instruction cache.
+        PROF(23)
 #pragma unroll 1
       for (int j = -1; j < w.ntiles && ok; ++j) {
         const int t0 = w.t_begin + j * T;
@@ -465,6 +472,28 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             for (int e = 0; e < 32; ++e) H[32 + e] = fmaf(H[32 + e], g, __uint_as_float(sv1[e]));
           }
         PROF(2)
+        }
+        // ---- c. next tile: prefix sum and Xd (the S MMA that read the Xd buffer was waited for in step a)
+        float cs_n = 0.f, tot_n = 0.f, cs2_n = 0.f;
+        if (have_next) {
+          const uint32_t itn = (j >= 0) ? it + 1 : it;
+          const float a = a_next, dtv = dt_next;
+          if (j + 2 < w.ntiles) {
+            a_next = Ag[(int64_t)(t0 + 2 * T + l) * sp.as[1]];
+            if (Dg) dt_next = Cvt<T16>::to_f(Dg[(int64_t)(t0 + 2 * T + l) * sp.dts[1]]);
+          }
+          scan_tile(a, itn & 1, cs_n, tot_n, cs2_n);
+          ok = cwait(&m->full_x[h][itn % kXStages], (itn / kXStages) & 1, STATUS_WAIT_TIMEOUT_TMA);
+          if (!ok) break;
+        PROF(14)
+          make_xd(itn % kXStages, cs_n, tot_n, dtv, Dg != nullptr);
+        PROF(15)
+          fence_proxy_async();
+          mbar_arrive(&m->bar_xd[h]);
+          if (!want_y) mbar_arrive(&m->empty_x[h][itn % kXStages]);   // nothing else reads X in state-only mode
+        }
+        PROF(16)
+        if (j >= 0) {
           if (want_y) {
             // ---- b. Y <- exp(cs_l) * (C.H) in place; the MMA of step d accumulates P.X on top
             ok = cwait(&m->bar_yo[h], it & 1, STATUS_WAIT_TIMEOUT_MMA);
@@ -490,13 +519,6 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         PROF(6)
           }
         }
-        // (all C.H MMAs that read the state copy have been waited for: the previous item's in its step b)
-        if (want_y && have_next) {
-          store_hb();
-          fence_proxy_async();
-          mbar_arrive(&m->bar_h[h]);
-        }
-        PROF(7)
         if (j >= 0) {
           if (want_y) {
             // ---- d. P = (C B^T) o exp(segsum), causal -> TMEM (A operand, 16-bit pairs)
@@ -504,49 +526,53 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             if (!ok) break;
         PROF(8)
             tc_fence_after();
-            // Decay mask per 32-token column block J (rolled loop: one copy of each case):
-            //   J == q (diagonal block): exp2(cs_l - cs_s), causal, one ex2 per element;
+            const uint32_t par = it & 1;
+            // Decay mask per 32-token column block J of this warp's 32 rows (block q is the diagonal one):
+            //   J == q: exp2(cs_l - cs_s), causal, one ex2 per element;
             //   J <  q: exp(cs_l - cs_s) = rf_J[l] * cf[s] with both factors <= 1 for non-positive
             //           log-decays (rf_J[l] = exp(cs_l - cs_end(J)), cf[s] = exp(cs_end(J) - cs_s)): two multiplies;
             //   J >  q: zero, written once (nothing else ever writes those TMEM columns).
-#pragma unroll 1
-            for (int J = 0; J < 4; ++J) {
+            {
+              // diagonal block first: its TMEM load is in flight while the factors are fetched
+              uint32_t gd[32];
+              tmem_ld32(tG + tlane + 32 * q, gd);
+              tmem_ld_wait();
               uint32_t pk[16];
-              if (J > q) {
-                if (it != 0) continue;
 #pragma unroll
-                for (int e = 0; e < 16; ++e) pk[e] = 0u;
-              } else {
-                uint32_t gv[32];
-                tmem_ld32(tG + tlane + 32 * J, gv);
-                const bool diag = (J == q);
-                const float4* fv = reinterpret_cast<const float4*>(diag ? &m->cs2[h][32 * J] : &m->cf[h][32 * J]);
-                const float rf = diag ? 0.f : ex2(cs2 - m->cs2[h][32 * J + 31]);
-                float4 fq[8];
+              for (int e2 = 0; e2 < 16; ++e2) {
+                // cs of the two columns comes from the lanes that own those rows
+                const float c0 = __shfl_sync(0xffffffffu, cs2, 2 * e2), c1 = __shfl_sync(0xffffffffu, cs2, 2 * e2 + 1);
+                const float v0 = __uint_as_float(gd[2 * e2]) * ex2(cs2 - c0);
+                const float v1 = __uint_as_float(gd[2 * e2 + 1]) * ex2(cs2 - c1);
+                pk[e2] = pack2<T16>(2 * e2 <= lane ? v0 : 0.f, 2 * e2 + 1 <= lane ? v1 : 0.f);
+              }
+              tmem_st16(tP + tlane + 16 * q, pk);
+            }
+#pragma unroll 1
+            for (int J = 0; J < q; ++J) {   // strictly below the diagonal
+              uint32_t gv[32];
+              tmem_ld32(tG + tlane + 32 * J, gv);
+              const float rf = ex2(cs2 - m->cend[h][par][J]);
+              float4 fq[8];
+              const float4* fv = reinterpret_cast<const float4*>(&m->cf[h][par][32 * J]);
 #pragma unroll
-                for (int e4 = 0; e4 < 8; ++e4) fq[e4] = fv[e4];   // shared-memory latency overlaps the TMEM load
-                tmem_ld_wait();
+              for (int e4 = 0; e4 < 8; ++e4) fq[e4] = fv[e4];
+              tmem_ld_wait();
+              uint32_t pk[16];
 #pragma unroll
-                for (int e4 = 0; e4 < 8; ++e4) {
-                  const float4 c4 = fq[e4];
-                  const float cc[4] = {c4.x, c4.y, c4.z, c4.w};
-                  float pv[4];
-#pragma unroll
-                  for (int r = 0; r < 4; ++r) {
-                    const int e = 4 * e4 + r;
-                    const float gval = __uint_as_float(gv[e]);
-                    if (diag) {
-                      const float val = gval * ex2(cs2 - cc[r]);
-                      pv[r] = (32 * J + e <= l) ? val : 0.f;
-                    } else {
-                      pv[r] = gval * (rf * cc[r]);
-                    }
-                  }
-                  pk[2 * e4] = pack2<T16>(pv[0], pv[1]);
-                  pk[2 * e4 + 1] = pack2<T16>(pv[2], pv[3]);
-                }
+              for (int e4 = 0; e4 < 8; ++e4) {
+                const float w0 = rf * fq[e4].x, w1 = rf * fq[e4].y, w2 = rf * fq[e4].z, w3 = rf * fq[e4].w;
+                pk[2 * e4] = pack2<T16>(__uint_as_float(gv[4 * e4]) * w0, __uint_as_float(gv[4 * e4 + 1]) * w1);
+                pk[2 * e4 + 1] = pack2<T16>(__uint_as_float(gv[4 * e4 + 2]) * w2, __uint_as_float(gv[4 * e4 + 3]) * w3);
               }
               tmem_st16(tP + tlane + 16 * J, pk);
+            }
+            if (it == 0) {
+              uint32_t pz[16];
+#pragma unroll
+              for (int e = 0; e < 16; ++e) pz[e] = 0u;
+#pragma unroll 1
+              for (int J = q + 1; J < 4; ++J) tmem_st16(tP + tlane + 16 * J, pz);
             }
         PROF(9)
             tmem_st_wait();
@@ -555,26 +581,13 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         PROF(10)
           }
         }
-        // ---- c. next tile: prefix sum and Xd (the S MMA that read the Xd buffer was waited for in step a)
-        float cs_n = 0.f, tot_n = 0.f, cs2_n = 0.f;
-        if (have_next) {
-          const uint32_t itn = (j >= 0) ? it + 1 : it;
-          const float a = a_next, dtv = dt_next;
-          if (j + 2 < w.ntiles) {
-            a_next = Ag[(int64_t)(t0 + 2 * T + l) * sp.as[1]];
-            if (Dg) dt_next = Cvt<T16>::to_f(Dg[(int64_t)(t0 + 2 * T + l) * sp.dts[1]]);
-          }
-          scan_tile(a, cs_n, tot_n, cs2_n);
-          ok = cwait(&m->full_x[h][itn % kXStages], (itn / kXStages) & 1, STATUS_WAIT_TIMEOUT_TMA);
-          if (!ok) break;
-        PROF(14)
-          make_xd(itn % kXStages, cs_n, tot_n, dtv, Dg != nullptr);
-        PROF(15)
+        // (all C.H MMAs that read the state copy have been waited for: the previous item's in its step b)
+        if (want_y && have_next) {
+          store_hb();
           fence_proxy_async();
-          mbar_arrive(&m->bar_xd[h]);
-          if (!want_y) mbar_arrive(&m->empty_x[h][itn % kXStages]);   // nothing else reads X in state-only mode
+          mbar_arrive(&m->bar_h[h]);
         }
-        PROF(16)
+        PROF(7)
         if (j >= 0) {
           if (want_y) {
             // ---- e. Y -> global
@@ -612,27 +625,21 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
               }
             }
         PROF(19)
-            __syncwarp();
-            {
-              const int cc = lane & 7;
-              T16* ybase = Yg + (int64_t)t0 * sp.ys[1] + cc * 8;
-              uint4 yv[8];
-#pragma unroll
-              for (int kq = 0; kq < 8; ++kq) {
-                const int r = lane_base + 4 * kq + (lane >> 3);
-                yv[kq] = lds128(ystage + r * 128 + ((cc ^ (r & 7)) << 4));
-              }
-#pragma unroll
-              for (int kq = 0; kq < 8; ++kq) {
-                const int r = lane_base + 4 * kq + (lane >> 3);
-                *reinterpret_cast<uint4*>(ybase + (int64_t)r * sp.ys[1]) = yv[kq];
-              }
-            }
-        PROF(20)
-            fence_proxy_async();   // generic writes to the stage are ordered before the TMA refill
-            mbar_arrive(&m->empty_x[h][xst]);
             tc_fence_before();
-            mbar_arrive(&m->bar_e[h]);
+            mbar_arrive(&m->bar_e[h]);   // the Y accumulator is read out: the next tile's C.H may overwrite it
+            fence_proxy_async();         // staged rows -> visible to the TMA engine
+            named_bar_sync(bar_id, 128);
+            if (l == 0) {
+              // The previous store must be done reading its stage before the producer may refill it.
+              if (store_pending) {
+                bulk_wait_read_all();
+                mbar_arrive(&m->empty_x[h][store_stage]);
+              }
+              tma_store_4d(&tmY, ystage, 0, hi, t0, w.bi);
+              bulk_commit();
+              store_pending = true;
+              store_stage = xst;
+            }
         PROF(21)
           }
           ++it;
@@ -670,6 +677,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           sp.fin_ld[unit * sp.finld_unit_stride + fseg * sp.finld_seg_stride] = asum0 + asum;
       }
     }
+    if (l == 0 && store_pending) bulk_wait_all();   // the last Y tile must have left shared memory
 #ifdef SSD_TC2_PROFILE
     if (blockIdx.x == 0 && h == 0 && (l == 0 || l == 96) && status) {
       for (int i = 0; i < 24; ++i) status[2 + 24 * (l / 96) + i] = (int)(prof[i] >> 4);   // cycles / 16
@@ -687,14 +695,14 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 }
 
 template <typename T16, int N>
-int launch_typed2(const CUtensorMap& tx, const CUtensorMap& tb, const CUtensorMap& tc, const Tc2Params& prm,
-                  cudaStream_t stream) {
+int launch_typed2(const CUtensorMap& tx, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& ty,
+                  const Tc2Params& prm, cudaStream_t stream) {
   auto kern = ssd_tc2_kernel<T16, N>;
   constexpr int smem = Layout2<N>::kBytes;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
     return SSD_ERR_CUDA;
   const int grid = std::min(prm.nitems, kSms);
-  kern<<<grid, kThreads2, smem, stream>>>(tx, tb, tc, prm);
+  kern<<<grid, kThreads2, smem, stream>>>(tx, tb, tc, ty, prm);
   return cudaGetLastError() == cudaSuccess ? SSD_OK : SSD_ERR_CUDA;
 }
 
@@ -754,19 +762,21 @@ int launch_tc2(const SsdArgs& a, const ScanParams& sp, cudaStream_t stream) {
   prm.sp = sp;
   prm.upairs = a.batch * (a.nheads / 2);
   prm.nitems = prm.upairs * sp.nseg;
-  CUtensorMap tx, tb, tc;
+  CUtensorMap tx, tb, tc, ty;
   if (!make_map(&tx, a.X, a.dtype, a.headdim, a.nheads, a.seqlen, a.batch, a.x_stride)) return SSD_ERR_CUDA;
   if (!make_map(&tb, a.B, a.dtype, a.dstate, a.ngroups, a.seqlen, a.batch, a.b_stride)) return SSD_ERR_CUDA;
   if (sp.compute_y) {
     if (!make_map(&tc, a.C, a.dtype, a.dstate, a.ngroups, a.seqlen, a.batch, a.c_stride)) return SSD_ERR_CUDA;
+    if (!make_map(&ty, a.Y, a.dtype, a.headdim, a.nheads, a.seqlen, a.batch, a.y_stride)) return SSD_ERR_CUDA;
   } else {
     tc = tb;
+    ty = tx;
   }
   if (a.dtype == SSD_DTYPE_BF16)
-    return a.dstate == 128 ? launch_typed2<__nv_bfloat16, 128>(tx, tb, tc, prm, stream)
-                           : launch_typed2<__nv_bfloat16, 64>(tx, tb, tc, prm, stream);
-  return a.dstate == 128 ? launch_typed2<__half, 128>(tx, tb, tc, prm, stream)
-                         : launch_typed2<__half, 64>(tx, tb, tc, prm, stream);
+    return a.dstate == 128 ? launch_typed2<__nv_bfloat16, 128>(tx, tb, tc, ty, prm, stream)
+                           : launch_typed2<__nv_bfloat16, 64>(tx, tb, tc, ty, prm, stream);
+  return a.dstate == 128 ? launch_typed2<__half, 128>(tx, tb, tc, ty, prm, stream)
+                         : launch_typed2<__half, 64>(tx, tb, tc, ty, prm, stream);
 }
 
 }  // namespace ssd

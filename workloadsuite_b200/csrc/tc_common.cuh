@@ -44,6 +44,21 @@ __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// Packed 16-bit multiply of two values by one scalar (both given as packed pairs).  The reference forms
+// X*dt and the decay-scaled operands in half precision too (model_ref.py:144,148).
+template <typename T16>
+__device__ __forceinline__ uint32_t mul2(uint32_t v, uint32_t s2);
+template <>
+__device__ __forceinline__ uint32_t mul2<__nv_bfloat16>(uint32_t v, uint32_t s2) {
+  __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&v), *reinterpret_cast<const __nv_bfloat162*>(&s2));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+template <>
+__device__ __forceinline__ uint32_t mul2<__half>(uint32_t v, uint32_t s2) {
+  __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&v), *reinterpret_cast<const __half2*>(&s2));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
