@@ -73,42 +73,88 @@ class SequenceShardedSSD:
 
     Rank r holds tokens ``[r*s/R, (r+1)*s/R)`` of every tensor.  ``forward`` returns
     the local Y shard.  Buffers for the exchange are allocated once per shape.
+
+    With ``cuda_graphs=True`` the two local phases (everything before and everything after
+    the all-gather) are captured into CUDA graphs the first time a given set of tensors is
+    seen and replayed afterwards; the collective itself is always launched normally.  The
+    returned Y is then the same tensor on every call with those inputs.
     """
 
     def __init__(self, group: Optional[dist.ProcessGroup] = None, scan_fn: Callable = _cuda_scan,
-                 fold_fn: Callable = _cuda_fold):
+                 fold_fn: Callable = _cuda_fold, cuda_graphs: bool = False):
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         self.scan_fn = scan_fn
         self.fold_fn = fold_fn
+        self.cuda_graphs = cuda_graphs
         self._send = None
         self._recv = None
+        self._graphs = {}
 
     def _buffers(self, numel: int, device):
         if self._send is None or self._send.numel() != numel or self._send.device != device:
             self._send = torch.empty(numel, dtype=torch.float32, device=device)
             self._recv = torch.empty(self.world * numel, dtype=torch.float32, device=device)
+            self._graphs.clear()
         return self._send, self._recv
 
-    def forward(self, X, A, B, C, chunk, dt=None, initial_states=None, **kw):
+    # phase 1: local scan from zero, final state and summed log-decay only, packed for the exchange
+    def _phase_local(self, X, A, B, C, chunk, dt, kw):
         b, s_loc, h, p = X.shape
         n = B.shape[3]
-        # phase 1: local scan from zero, final state and summed log-decay only
         F, D = self.scan_fn(X, A, B, C, chunk, dt=dt, initial_states=None, state_only=True, **kw)
         ns, nd = F.numel(), D.numel()
         send, recv = self._buffers(ns + nd, F.device)
         send[:ns].copy_(F.reshape(-1))
         send[ns:].copy_(D.reshape(-1))
-        # phase 2: the only collective -- every rank's (state, log-decay) to every rank
-        dist.all_gather_into_tensor(recv, send, group=self.group)
-        recv = recv.view(self.world, ns + nd)
+        return (b, h, n, p, ns, nd)
+
+    # phase 3: fold the predecessors, then the real scan seeded with the result
+    def _phase_seeded(self, X, A, B, C, chunk, dt, initial_states, dims, kw):
+        b, h, n, p, ns, nd = dims
+        recv = self._recv.view(self.world, ns + nd)
         states = recv[:, :ns].unflatten(1, (b, h, n, p))
         lds = recv[:, ns:].unflatten(1, (b, h))
-        # phase 3: fold the predecessors, then the real scan seeded with the result
         # (initial_states, the state before token 0 of the whole sequence, is replicated on all ranks)
         h_in = initial_states if self.rank == 0 else self.fold_fn(states, lds, self.rank, initial_states)
         return self.scan_fn(X, A, B, C, chunk, dt=dt, initial_states=h_in, state_only=False, **kw)
+
+    def forward(self, X, A, B, C, chunk, dt=None, initial_states=None, **kw):
+        if self.cuda_graphs and X.is_cuda:
+            return self._forward_graphed(X, A, B, C, chunk, dt, initial_states, kw)
+        dims = self._phase_local(X, A, B, C, chunk, dt, kw)
+        # phase 2: the only collective -- every rank's (state, log-decay) to every rank
+        dist.all_gather_into_tensor(self._recv, self._send, group=self.group)
+        return self._phase_seeded(X, A, B, C, chunk, dt, initial_states, dims, kw)
+
+    def _forward_graphed(self, X, A, B, C, chunk, dt, initial_states, kw):
+        out = kw.get("out")
+        key = (X.data_ptr(), A.data_ptr(), B.data_ptr(), C.data_ptr(), chunk,
+               None if dt is None else dt.data_ptr(), None if initial_states is None else initial_states.data_ptr(),
+               None if out is None else out.data_ptr(), tuple(sorted((k, str(v)) for k, v in kw.items() if k != "out")))
+        entry = self._graphs.get(key)
+        if entry is None:
+            # one ordinary run first: allocates workspaces and exchange buffers outside any capture
+            dims = self._phase_local(X, A, B, C, chunk, dt, kw)
+            dist.all_gather_into_tensor(self._recv, self._send, group=self.group)
+            self._phase_seeded(X, A, B, C, chunk, dt, initial_states, dims, kw)
+            torch.cuda.synchronize(X.device)
+            cap = torch.cuda.Stream(device=X.device)
+            g1, g2 = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+            with torch.cuda.stream(cap):
+                with torch.cuda.graph(g1, stream=cap):
+                    dims = self._phase_local(X, A, B, C, chunk, dt, kw)
+                with torch.cuda.graph(g2, stream=cap):
+                    Y = self._phase_seeded(X, A, B, C, chunk, dt, initial_states, dims, kw)
+            torch.cuda.synchronize(X.device)
+            entry = (g1, g2, Y)
+            self._graphs[key] = entry
+        g1, g2, Y = entry
+        g1.replay()
+        dist.all_gather_into_tensor(self._recv, self._send, group=self.group)
+        g2.replay()
+        return Y
 
 
 def sequence_sharded_forward(X, A, B, C, chunk, group=None, dt=None, initial_states=None, **kw):
