@@ -51,7 +51,7 @@ struct Misc2 {
   uint64_t full_x[2][kXStages], empty_x[2][kXStages];
   uint64_t bar_g;
   uint64_t bar_yo[2], bar_s[2], bar_y[2];            // tcgen05.commit arrivals
-  uint64_t bar_xd[2], bar_h[2], bar_p[2], bar_e[2];  // 128 compute-thread arrivals
+  uint64_t bar_xd[2], bar_h[2], bar_p[2], bar_e[2];  // one arrival per compute warp of the head
   uint32_t tmem_base;
   volatile int abort_flag;
   float wsum[2][4];
@@ -132,11 +132,12 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       // has served as the source of the TMA store of Y)
       for (int s = 0; s < kXStages; ++s) {
         mbar_init(&m->full_x[h][s], 1);
-        mbar_init(&m->empty_x[h][s], want_y ? 1 : 128);   // Y mode: the thread that issued the TMA store of Y
+        mbar_init(&m->empty_x[h][s], want_y ? 1 : 4);   // Y mode: the thread that issued the TMA store of Y
       }
       mbar_init(&m->bar_yo[h], 1); mbar_init(&m->bar_s[h], 1); mbar_init(&m->bar_y[h], 1);
-      mbar_init(&m->bar_xd[h], 128); mbar_init(&m->bar_h[h], 128); mbar_init(&m->bar_p[h], 128);
-      mbar_init(&m->bar_e[h], 128);
+      // one arrival per compute warp (lane 0, after a warp barrier): 4 warps per head
+      mbar_init(&m->bar_xd[h], 4); mbar_init(&m->bar_h[h], 4); mbar_init(&m->bar_p[h], 4);
+      mbar_init(&m->bar_e[h], 4);
     }
     m->abort_flag = 0;
     fence_mbar_init();
@@ -306,6 +307,12 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     bool ok = true;
     auto cwait = [&](uint64_t* bar, uint32_t parity, int code) {
       return __all_sync(0xffffffffu, wait2(bar, parity, m, code, status)) != 0;
+    };
+    // One arrival per warp: every lane has issued its fences, the warp barrier orders their writes before
+    // lane 0's arrive (128 per-thread arrivals on one mbarrier cost several hundred cycles per hand-off).
+    auto warp_arrive = [&](uint64_t* bar) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar);
     };
 
 #ifdef SSD_TC2_PROFILE
@@ -494,8 +501,8 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           make_xd(itn % kXStages, cs_n, tot_n, dtv, Dg != nullptr);
         PROF(15)
           fence_proxy_async();
-          mbar_arrive(&m->bar_xd[h]);
-          if (!want_y) mbar_arrive(&m->empty_x[h][itn % kXStages]);   // nothing else reads X in state-only mode
+          warp_arrive(&m->bar_xd[h]);
+          if (!want_y) warp_arrive(&m->empty_x[h][itn % kXStages]);   // nothing else reads X in state-only mode
         }
         PROF(16)
         // ---- state entering the item (after the first tile's Xd is on its way to the S MMA: the wait for a
@@ -629,7 +636,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         PROF(9)
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(&m->bar_p[h]);
+            warp_arrive(&m->bar_p[h]);
         PROF(10)
           }
         }
@@ -637,7 +644,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         if (want_y && have_next) {
           store_hb();
           fence_proxy_async();
-          mbar_arrive(&m->bar_h[h]);
+          warp_arrive(&m->bar_h[h]);
         }
         PROF(7)
         if (j >= 0) {
@@ -678,7 +685,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             }
         PROF(19)
             tc_fence_before();
-            mbar_arrive(&m->bar_e[h]);   // the Y accumulator is read out: the next tile's C.H may overwrite it
+            warp_arrive(&m->bar_e[h]);   // the Y accumulator is read out: the next tile's C.H may overwrite it
             fence_proxy_async();         // staged rows -> visible to the TMA engine
             named_bar_sync(bar_id, 128);
             if (l == 0) {
