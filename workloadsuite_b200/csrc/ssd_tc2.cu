@@ -50,8 +50,9 @@ struct Misc2 {
   uint64_t full_b, full_c, empty_b, empty_c;
   uint64_t full_x[2][kXStages], empty_x[2][kXStages];
   uint64_t bar_g;
-  uint64_t bar_yo[2], bar_s[2], bar_y[2];            // tcgen05.commit arrivals
-  uint64_t bar_xd[2], bar_h[2], bar_p[2], bar_e[2];  // one arrival per compute warp of the head
+  uint64_t bar_yo, bar_s, bar_y[2];   // tcgen05.commit arrivals (the S and C.H MMAs serve both heads at once)
+  uint64_t bar_xd, bar_h, bar_e;      // one arrival per compute warp of either head (8)
+  uint64_t bar_p[2];                  // one arrival per compute warp of the head (4)
   uint32_t tmem_base;
   volatile int abort_flag;
   float wsum[2][4];
@@ -89,6 +90,7 @@ __device__ __forceinline__ Item decode_item(const ScanParams& sp, int upairs, in
 
 // Deliberately not inlined: the kernel's steady-state loop has to stay small enough for the instruction cache.
 __device__ __forceinline__ bool wait2(uint64_t* bar, uint32_t parity, Misc2* m, int code, int32_t* status) {
+  if (mbar_try_wait(bar, parity)) return true;   // the common case in steady state: no clock read, no sleep
   const long long t0 = clock64();
   while (!mbar_try_wait_sleep(bar, parity, 200000u)) {
     if (m->abort_flag) return false;
@@ -100,6 +102,15 @@ __device__ __forceinline__ bool wait2(uint64_t* bar, uint32_t parity, Misc2* m, 
   }
   return true;
 }
+
+#ifdef SSD_TC2_TRACE
+// debug build: time stamps of pipeline events of CTA 0 for tiles [kTr0, kTr0+kTrN) into status[256...]
+constexpr int kTr0 = 20, kTrN = 6, kTrEv = 24;
+#define TRACE(ev, tile) { if (blockIdx.x == 0 && status && (int)(tile) >= kTr0 && (int)(tile) < kTr0 + kTrN) \
+    status[256 + ((int)(tile) - kTr0) * kTrEv + (ev)] = (int)(clock64() & 0x7fffffff); }
+#else
+#define TRACE(ev, tile) {}
+#endif
 
 template <typename T16, int N>
 __global__ void __launch_bounds__(kThreads2, 1)
@@ -124,9 +135,11 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 
   if (tid == 0) {
     mbar_init(&m->full_b, 1); mbar_init(&m->full_c, 1);
-    // B is released by the G issuer and both heads' S; C by the G issuer and both heads' C.H
-    mbar_init(&m->empty_b, want_y ? 3 : 2); mbar_init(&m->empty_c, 3);
+    // B is released by the G MMA and the S MMA; C by the G MMA and the C.H MMA
+    mbar_init(&m->empty_b, want_y ? 2 : 1); mbar_init(&m->empty_c, 2);
     mbar_init(&m->bar_g, 1);
+    mbar_init(&m->bar_yo, 1); mbar_init(&m->bar_s, 1);
+    mbar_init(&m->bar_xd, 8); mbar_init(&m->bar_h, 8); mbar_init(&m->bar_e, 8);
     for (int h = 0; h < 2; ++h) {
       // an X stage is handed back by the head's warpgroup once it is done with it (in Y mode: after the stage
       // has served as the source of the TMA store of Y)
@@ -134,10 +147,8 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         mbar_init(&m->full_x[h][s], 1);
         mbar_init(&m->empty_x[h][s], want_y ? 1 : 4);   // Y mode: the thread that issued the TMA store of Y
       }
-      mbar_init(&m->bar_yo[h], 1); mbar_init(&m->bar_s[h], 1); mbar_init(&m->bar_y[h], 1);
-      // one arrival per compute warp (lane 0, after a warp barrier): 4 warps per head
-      mbar_init(&m->bar_xd[h], 4); mbar_init(&m->bar_h[h], 4); mbar_init(&m->bar_p[h], 4);
-      mbar_init(&m->bar_e[h], 4);
+      mbar_init(&m->bar_y[h], 1);
+      mbar_init(&m->bar_p[h], 4);   // one arrival per compute warp (lane 0, after a warp barrier)
     }
     m->abort_flag = 0;
     fence_mbar_init();
@@ -168,6 +179,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             if (!ok) break;
             mbar_expect_tx(&m->full_x[h][st], kBlk);
             tma_load_4d(smem + L::oX + (kXStages * h + st) * kBlk, &tmX, &m->full_x[h][st], 0, w.h0 + h, t0, w.bi);
+            if (h == 0) TRACE(14, it)
           }
           if (!ok) break;
           if (want_y) {
@@ -177,6 +189,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 #pragma unroll
             for (int kb = 0; kb < NB; ++kb)
               tma_load_4d(smem + L::oC + kb * kBlk, &tmC, &m->full_c, 64 * kb, w.gi, t0, w.bi);
+            TRACE(15, it)
           }
           if (it > 0) ok = wait2(&m->empty_b, (it - 1) & 1, m, STATUS_WAIT_TIMEOUT_MMA, status);
           if (!ok) break;
@@ -184,6 +197,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 #pragma unroll
           for (int kb = 0; kb < NB; ++kb)
             tma_load_4d(smem + L::oB + kb * kBlk, &tmB, &m->full_b, 64 * kb, w.gi, t0, w.bi);
+          TRACE(16, it)
         }
       }
       if (m->abort_flag && it > 0) {
@@ -221,72 +235,89 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             const uint32_t off = (kk >> 2) * kBlk + (kk & 3) * 32;
             umma_ss(tG, umma_desc(dK, sC + off), umma_desc(dK, sB + off), idG, kk > 0);
           }
+          TRACE(13, k)
           umma_commit(&m->bar_g);
           umma_commit(&m->empty_c);
           umma_commit(&m->empty_b);
         }
       }
-    } else if ((warp == 2 || warp == 3) && lane == 0) {
-      // ---------------------------------------------------------------- per-head MMA issuer: Yo, S, Yd of head h
-      // Blocking waits, in the order the head's compute warpgroup raises the barriers.
-      const int h = warp - 2;
+    } else if (warp == 2 && lane == 0) {
+      // ---------------------------------------------------------------- MMA issuer for S = B^T.[Xd0|Xd1] and Y = C.[H0|H1]
+      // The two heads' Xd (and state copies) lie one 64-column block apart in shared memory, so one
+      // N = 128 MMA serves both heads; it costs the tensor pipe what the N = 64 one does.
       constexpr int fmt = std::is_same<T16, __nv_bfloat16>::value ? 1 : 0;
-      constexpr uint32_t idKM = umma_idesc(128, 64, fmt, 0, 1);
-      constexpr uint32_t idMM = umma_idesc(128, 64, fmt, 1, 1);
+      constexpr uint32_t idKM = umma_idesc(128, 128, fmt, 0, 1);
+      constexpr uint32_t idMM = umma_idesc(128, 128, fmt, 1, 1);
       constexpr uint64_t dK = umma_desc_base(16, 1024);
-      constexpr uint64_t dMN = umma_desc_base(kBlk, 1024);
-      const uint32_t tS = tb + 128 + 192 * h, tP = tS + 64, tY = tS + 128;
-      const uint32_t sHh = sH + h * (N * 128), sXdh = sXd + h * kBlk;
+      constexpr uint64_t dMN = umma_desc_base(kBlk, 1024);       // B tile; [Xd0|Xd1]
+      constexpr uint64_t dMNh = umma_desc_base(N * 128, 1024);   // [H0|H1]
+      const uint32_t tS = tb + 128, tY = tb + 256;
       bool ok = true;
-      auto issue_yo = [&](uint32_t k) {   // Y <- C . H
-        ok = ok && wait2(&m->full_c, k & 1, m, STATUS_WAIT_TIMEOUT_TMA, status) &&
-             wait2(&m->bar_h[h], k & 1, m, STATUS_WAIT_TIMEOUT_SYNC, status);
-        if (ok && k > 0) ok = wait2(&m->bar_e[h], (k - 1) & 1, m, STATUS_WAIT_TIMEOUT_SYNC, status);
-        if (!ok) return;
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < KN; ++kk) {
-          const uint32_t off = (kk >> 2) * kBlk + (kk & 3) * 32;
-          umma_ss(tY, umma_desc(dK, sC + off), umma_desc(dMN, sHh + kk * 2048), idKM, kk > 0);
-        }
-        umma_commit(&m->bar_yo[h]);
-        umma_commit(&m->empty_c);
-      };
-      auto issue_s = [&](uint32_t k) {    // S <- B^T . Xd
-        ok = ok && wait2(&m->full_b, k & 1, m, STATUS_WAIT_TIMEOUT_TMA, status) &&
-             wait2(&m->bar_xd[h], k & 1, m, STATUS_WAIT_TIMEOUT_SYNC, status);
-        if (!ok) return;
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < KT; ++kk)
-          umma_ss(tS, umma_desc(dMN, sB + kk * 2048), umma_desc(dMN, sXdh + kk * 2048), idMM, kk > 0);
-        umma_commit(&m->bar_s[h]);
-        umma_commit(&m->empty_b);
-      };
-      auto issue_yd = [&](uint32_t k) {   // Y += P . X
-        const uint32_t st = k % kXStages;
-        ok = ok && wait2(&m->bar_p[h], k & 1, m, STATUS_WAIT_TIMEOUT_SYNC, status) &&
-             wait2(&m->full_x[h][st], (k / kXStages) & 1, m, STATUS_WAIT_TIMEOUT_TMA, status);
-        if (!ok) return;
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < KT; ++kk)
-          umma_ts(tY, tP + 8 * kk, umma_desc(dMN, sX + (kXStages * h + st) * kBlk + kk * 2048), idKM, 1);
-        umma_commit(&m->bar_y[h]);
-      };
-      // One uniform loop (a single copy of each task keeps the code small): per item,
-      //   j = 0..nt:  Yd(k0+j-1) if j > 0;  S(k0+j) if j < nt;  Yo(k0+j) if j < nt
-      // which is the order the head's warpgroup raises the barriers these tasks wait on.
       uint32_t k0 = 0;   // running tile ordinal of the item's first tile
       for (int item = blockIdx.x; item < prm.nitems && ok; item += gridDim.x) {
         const int nt = decode_item(sp, prm.upairs, item).ntiles;
 #pragma unroll 1
-        for (int j = 0; j <= nt && ok; ++j) {
-          if (want_y && j > 0) issue_yd(k0 + j - 1);
-          if (j < nt) issue_s(k0 + j);
-          if (want_y && j < nt) issue_yo(k0 + j);
+        for (int j = 0; j < nt && ok; ++j) {
+          const uint32_t k = k0 + j;
+          // S <- B^T . Xd
+          ok = wait2(&m->full_b, k & 1, m, STATUS_WAIT_TIMEOUT_TMA, status) &&
+               wait2(&m->bar_xd, k & 1, m, STATUS_WAIT_TIMEOUT_SYNC, status);
+          if (!ok) break;
+          TRACE(22, k)
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < KT; ++kk)
+            umma_ss(tS, umma_desc(dMN, sB + kk * 2048), umma_desc(dMN, sXd + kk * 2048), idMM, kk > 0);
+          TRACE(10, k)
+          umma_commit(&m->bar_s);
+          umma_commit(&m->empty_b);
+          if (!want_y) continue;
+          // Y <- C . H
+          ok = wait2(&m->full_c, k & 1, m, STATUS_WAIT_TIMEOUT_TMA, status) &&
+               wait2(&m->bar_h, k & 1, m, STATUS_WAIT_TIMEOUT_SYNC, status);
+          if (ok && k > 0) ok = wait2(&m->bar_e, (k - 1) & 1, m, STATUS_WAIT_TIMEOUT_SYNC, status);
+          if (!ok) break;
+          TRACE(21, k)
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < KN; ++kk) {
+            const uint32_t off = (kk >> 2) * kBlk + (kk & 3) * 32;
+            umma_ss(tY, umma_desc(dK, sC + off), umma_desc(dMNh, sH + kk * 2048), idKM, kk > 0);
+          }
+          TRACE(12, k)
+          umma_commit(&m->bar_yo);
+          umma_commit(&m->empty_c);
         }
         k0 += nt;
+      }
+    } else if (warp == 3 && lane == 0) {
+      // ---------------------------------------------------------------- MMA issuer for Y_h += P_h . X_h, head 0 then head 1
+      if (want_y) {
+        constexpr int fmt = std::is_same<T16, __nv_bfloat16>::value ? 1 : 0;
+        constexpr uint32_t idKM = umma_idesc(128, 64, fmt, 0, 1);
+        constexpr uint64_t dMN = umma_desc_base(kBlk, 1024);
+        uint32_t ttot = 0;
+        for (int item = blockIdx.x; item < prm.nitems; item += gridDim.x)
+          ttot += decode_item(sp, prm.upairs, item).ntiles;
+        bool ok = true;
+#pragma unroll 1
+        for (uint32_t k = 0; k < ttot && ok; ++k) {
+          const uint32_t st = k % kXStages;
+#pragma unroll 1
+          for (int h = 0; h < 2 && ok; ++h) {
+            ok = wait2(&m->bar_p[h], k & 1, m, STATUS_WAIT_TIMEOUT_SYNC, status) &&
+                 wait2(&m->full_x[h][st], (k / kXStages) & 1, m, STATUS_WAIT_TIMEOUT_TMA, status);
+            if (!ok) break;
+            if (h == 0) TRACE(20, k)
+            tc_fence_after();
+            const uint32_t tY = tb + 256 + 64 * h, tP = tb + 384 + 64 * h;
+#pragma unroll
+            for (int kk = 0; kk < KT; ++kk)
+              umma_ts(tY, tP + 8 * kk, umma_desc(dMN, sX + (kXStages * h + st) * kBlk + kk * 2048), idKM, 1);
+            if (h == 0) TRACE(11, k)
+            umma_commit(&m->bar_y[h]);
+          }
+        }
       }
     }
   } else {
@@ -299,7 +330,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     const uint32_t tlane = (uint32_t)lane_base << 16;
     const uint32_t swz = (uint32_t)(l & 7);
     const bool owns_state = lane_base < N;
-    const uint32_t tS = tb + 128 + 192 * h, tP = tS + 64, tY = tS + 128;
+    const uint32_t tS = tb + 128 + 64 * h, tY = tb + 256 + 64 * h, tP = tb + 384 + 64 * h;
     const uint32_t sHh = sH + h * (N * 128), sXdh = sXd + h * kBlk;
     const int bar_id = 1 + h;
 
@@ -322,6 +353,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 #else
 #define PROF(i)
 #endif
+#define CTRACE(ev) { if (h == 0 && l == 96) TRACE(ev, it) }
     float H[P];
     float cs = 0.f, tot = 0.f, cs2 = 0.f;   // of the tile whose P / Y is being produced
     float a_next = 0.f, dt_next = 1.f;   // log-decay / dt of this thread's row in the next tile to be scanned
@@ -388,6 +420,69 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       }
     };
 
+    // ---- e. Y -> global, for the tile whose P.X MMA was started one step earlier (its latency is spent in the
+    //      next tile's state update).  Returns false when a wait gave up.
+    bool y_pending = false;
+    uint32_t y_it = 0;
+    int y_hi = 0, y_t0 = 0, y_bi = 0;
+    auto finish_y = [&]() -> bool {
+      PROF(20)
+      if (!cwait(&m->bar_y[h], y_it & 1, STATUS_WAIT_TIMEOUT_MMA)) return false;
+      if (h == 0 && l == 96) TRACE(8, y_it)
+      PROF(17)
+      tc_fence_after();
+      // The X stage of that tile is dead (its P.X MMA is complete): stage the 16-bit Y rows there; one
+      // thread then hands the whole tile to the TMA engine.
+      const uint32_t xst = y_it % kXStages;
+      const uint32_t ystage = sX + (kXStages * h + xst) * kBlk;
+      {
+        uint32_t y0[32], y1[32];
+        tmem_ld32(tY + tlane, y0);
+        tmem_ld32(tY + tlane + 32, y1);
+        tmem_ld_wait();
+      PROF(18)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint4 o;
+          o.x = pack2<T16>(__uint_as_float(y0[8 * c + 0]), __uint_as_float(y0[8 * c + 1]));
+          o.y = pack2<T16>(__uint_as_float(y0[8 * c + 2]), __uint_as_float(y0[8 * c + 3]));
+          o.z = pack2<T16>(__uint_as_float(y0[8 * c + 4]), __uint_as_float(y0[8 * c + 5]));
+          o.w = pack2<T16>(__uint_as_float(y0[8 * c + 6]), __uint_as_float(y0[8 * c + 7]));
+          sts128(ystage + l * 128 + ((c ^ swz) << 4), o);
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint4 o;
+          o.x = pack2<T16>(__uint_as_float(y1[8 * c + 0]), __uint_as_float(y1[8 * c + 1]));
+          o.y = pack2<T16>(__uint_as_float(y1[8 * c + 2]), __uint_as_float(y1[8 * c + 3]));
+          o.z = pack2<T16>(__uint_as_float(y1[8 * c + 4]), __uint_as_float(y1[8 * c + 5]));
+          o.w = pack2<T16>(__uint_as_float(y1[8 * c + 6]), __uint_as_float(y1[8 * c + 7]));
+          sts128(ystage + l * 128 + (((4 + c) ^ swz) << 4), o);
+        }
+      }
+      PROF(19)
+      tc_fence_before();
+      if (h == 0 && l == 96) TRACE(9, y_it)
+      warp_arrive(&m->bar_e);   // the Y accumulator is read out: the next tile's C.H may overwrite it
+      fence_proxy_async();         // staged rows -> visible to the TMA engine
+      named_bar_sync(bar_id, 128);
+      if (l == 0) {
+        // The previous store must be done reading its stage before the producer may refill it.
+        if (store_pending) {
+          bulk_wait_read_all();
+          mbar_arrive(&m->empty_x[h][store_stage]);
+        }
+        tma_store_4d(&tmY, ystage, 0, y_hi, y_t0, y_bi);
+        bulk_commit();
+        store_pending = true;
+        store_stage = xst;
+      }
+      if (h == 0 && l == 96) TRACE(17, y_it)
+      PROF(21)
+      y_pending = false;
+      return true;
+    };
+
     for (int item = blockIdx.x; item < prm.nitems && ok; item += gridDim.x) {
       const Item w = decode_item(sp, prm.upairs, item);
       if (w.ntiles == 0) continue;
@@ -395,7 +490,6 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       const int64_t unit = (int64_t)w.bi * sp.nheads + hi;
       const float* Ag = sp.A + w.bi * sp.as[0] + hi * sp.as[2];
       const T16* Dg = sp.dt ? static_cast<const T16*>(sp.dt) + w.bi * sp.dts[0] + hi * sp.dts[2] : nullptr;
-      T16* Yg = want_y ? static_cast<T16*>(sp.Y) + w.bi * sp.ys[0] + hi * sp.ys[2] : nullptr;
 
       float asum0 = 0.f;   // log-decay summed over the earlier segments of a chained sequence
       asum = 0.f;
@@ -418,8 +512,9 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         if (j >= 0) {
           // ---- a. state: H <- exp(cs_last) H + S
         PROF(22)
-          ok = cwait(&m->bar_s[h], it & 1, STATUS_WAIT_TIMEOUT_MMA);
+          ok = cwait(&m->bar_s, it & 1, STATUS_WAIT_TIMEOUT_MMA);
           if (!ok) break;
+          CTRACE(0)
         PROF(0)
           tc_fence_after();
           {
@@ -485,6 +580,10 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             }
           }
         }
+        if (y_pending) {   // (j == -1: the previous item's last tile)
+          ok = finish_y();
+          if (!ok) break;
+        }
         // ---- c. next tile: prefix sum and Xd (the S MMA that read the Xd buffer was waited for in step a)
         float cs_n = 0.f, tot_n = 0.f, cs2_n = 0.f;
         if (have_next) {
@@ -495,13 +594,16 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             if (Dg) dt_next = Cvt<T16>::to_f(Dg[(int64_t)(t0 + 2 * T + l) * sp.dts[1]]);
           }
           scan_tile(a, itn & 1, cs_n, tot_n, cs2_n);
+          if (h == 0 && l == 96) TRACE(18, itn)
           ok = cwait(&m->full_x[h][itn % kXStages], (itn / kXStages) & 1, STATUS_WAIT_TIMEOUT_TMA);
           if (!ok) break;
+          if (h == 0 && l == 96) TRACE(19, itn)
         PROF(14)
           make_xd(itn % kXStages, cs_n, tot_n, dtv, Dg != nullptr);
         PROF(15)
           fence_proxy_async();
-          warp_arrive(&m->bar_xd[h]);
+          warp_arrive(&m->bar_xd);
+          if (h == 0 && l == 96) TRACE(2, itn)
           if (!want_y) warp_arrive(&m->empty_x[h][itn % kXStages]);   // nothing else reads X in state-only mode
         }
         PROF(16)
@@ -552,37 +654,19 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             for (int j = 0; j < P; ++j) H[j] = 0.f;
           }
         }
-        if (j >= 0) {
-          if (want_y) {
-            // ---- b. Y <- exp(cs_l) * (C.H) in place; the MMA of step d accumulates P.X on top
-            ok = cwait(&m->bar_yo[h], it & 1, STATUS_WAIT_TIMEOUT_MMA);
-            if (!ok) break;
-        PROF(3)
-            tc_fence_after();
-            const float el = ex2(cs2);
-            {
-              uint32_t y0[32], y1[32];
-              tmem_ld32(tY + tlane, y0);
-              tmem_ld32(tY + tlane + 32, y1);
-              tmem_ld_wait();
-        PROF(4)
-#pragma unroll
-              for (int e = 0; e < 32; ++e) y0[e] = __float_as_uint(__uint_as_float(y0[e]) * el);
-              tmem_st32(tY + tlane, y0);
-#pragma unroll
-              for (int e = 0; e < 32; ++e) y1[e] = __float_as_uint(__uint_as_float(y1[e]) * el);
-              tmem_st32(tY + tlane + 32, y1);
-            }
-        PROF(5)
-            tmem_st_wait();
-        PROF(6)
-          }
+        if (l == 0 && store_pending) {
+          // the Y store issued in the previous tile's step e has finished reading its stage by now: hand it back
+          bulk_wait_read_all();
+          mbar_arrive(&m->empty_x[h][store_stage]);
+          store_pending = false;
         }
         if (j >= 0) {
           if (want_y) {
             // ---- d. P = (C B^T) o exp(segsum), causal -> TMEM (A operand, 16-bit pairs)
+            CTRACE(4)
             ok = cwait(&m->bar_g, it & 1, STATUS_WAIT_TIMEOUT_MMA);
             if (!ok) break;
+            CTRACE(5)
         PROF(8)
             tc_fence_after();
             const uint32_t par = it & 1;
@@ -634,9 +718,34 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
               for (int J = q + 1; J < 4; ++J) tmem_st16(tP + tlane + 16 * J, pz);
             }
         PROF(9)
+            // ---- b. Y <- exp(cs_l) * (C.H) in place (after P: the C.H MMA could only start once the previous
+            //      tile's Y had been read out, so it runs under step d); the P.X MMA accumulates on top
+            CTRACE(1)
+            ok = cwait(&m->bar_yo, it & 1, STATUS_WAIT_TIMEOUT_MMA);
+            if (!ok) break;
+            CTRACE(3)
+        PROF(3)
+            tc_fence_after();
+            const float el = ex2(cs2);
+            {
+              uint32_t y0[32], y1[32];
+              tmem_ld32(tY + tlane, y0);
+              tmem_ld32(tY + tlane + 32, y1);
+              tmem_ld_wait();
+        PROF(4)
+#pragma unroll
+              for (int e = 0; e < 32; ++e) y0[e] = __float_as_uint(__uint_as_float(y0[e]) * el);
+              tmem_st32(tY + tlane, y0);
+#pragma unroll
+              for (int e = 0; e < 32; ++e) y1[e] = __float_as_uint(__uint_as_float(y1[e]) * el);
+              tmem_st32(tY + tlane + 32, y1);
+            }
+        PROF(5)
             tmem_st_wait();
+        PROF(6)
             tc_fence_before();
-            warp_arrive(&m->bar_p[h]);
+            warp_arrive(&m->bar_p[h]);   // P is written and Y is scaled: the P.X MMA may run
+            CTRACE(6)
         PROF(10)
           }
         }
@@ -644,62 +753,14 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         if (want_y && have_next) {
           store_hb();
           fence_proxy_async();
-          warp_arrive(&m->bar_h[h]);
+          warp_arrive(&m->bar_h);
+          if (h == 0 && l == 96) TRACE(7, (j >= 0 ? it + 1 : it))
         }
         PROF(7)
         if (j >= 0) {
           if (want_y) {
-            // ---- e. Y -> global
-            ok = cwait(&m->bar_y[h], it & 1, STATUS_WAIT_TIMEOUT_MMA);
-            if (!ok) break;
-        PROF(17)
-            tc_fence_after();
-            // The X stage of this tile is dead (its P.X MMA is complete): stage the 16-bit Y rows there,
-            // then each warp copies its own 32 rows out with full 128-byte lines per 8 lanes.
-            const uint32_t xst = it % kXStages;
-            const uint32_t ystage = sX + (kXStages * h + xst) * kBlk;
-            {
-              uint32_t y0[32], y1[32];
-              tmem_ld32(tY + tlane, y0);
-              tmem_ld32(tY + tlane + 32, y1);
-              tmem_ld_wait();
-        PROF(18)
-#pragma unroll
-              for (int c = 0; c < 4; ++c) {
-                uint4 o;
-                o.x = pack2<T16>(__uint_as_float(y0[8 * c + 0]), __uint_as_float(y0[8 * c + 1]));
-                o.y = pack2<T16>(__uint_as_float(y0[8 * c + 2]), __uint_as_float(y0[8 * c + 3]));
-                o.z = pack2<T16>(__uint_as_float(y0[8 * c + 4]), __uint_as_float(y0[8 * c + 5]));
-                o.w = pack2<T16>(__uint_as_float(y0[8 * c + 6]), __uint_as_float(y0[8 * c + 7]));
-                sts128(ystage + l * 128 + ((c ^ swz) << 4), o);
-              }
-#pragma unroll
-              for (int c = 0; c < 4; ++c) {
-                uint4 o;
-                o.x = pack2<T16>(__uint_as_float(y1[8 * c + 0]), __uint_as_float(y1[8 * c + 1]));
-                o.y = pack2<T16>(__uint_as_float(y1[8 * c + 2]), __uint_as_float(y1[8 * c + 3]));
-                o.z = pack2<T16>(__uint_as_float(y1[8 * c + 4]), __uint_as_float(y1[8 * c + 5]));
-                o.w = pack2<T16>(__uint_as_float(y1[8 * c + 6]), __uint_as_float(y1[8 * c + 7]));
-                sts128(ystage + l * 128 + (((4 + c) ^ swz) << 4), o);
-              }
-            }
-        PROF(19)
-            tc_fence_before();
-            warp_arrive(&m->bar_e[h]);   // the Y accumulator is read out: the next tile's C.H may overwrite it
-            fence_proxy_async();         // staged rows -> visible to the TMA engine
-            named_bar_sync(bar_id, 128);
-            if (l == 0) {
-              // The previous store must be done reading its stage before the producer may refill it.
-              if (store_pending) {
-                bulk_wait_read_all();
-                mbar_arrive(&m->empty_x[h][store_stage]);
-              }
-              tma_store_4d(&tmY, ystage, 0, hi, t0, w.bi);
-              bulk_commit();
-              store_pending = true;
-              store_stage = xst;
-            }
-        PROF(21)
+            y_pending = true;
+            y_it = it; y_hi = hi; y_t0 = t0; y_bi = w.bi;
           }
           ++it;
         }
@@ -708,6 +769,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       if (!ok) break;
 
     }
+    if (ok && y_pending) ok = finish_y();
     if (l == 0 && store_pending) bulk_wait_all();   // the last Y tile must have left shared memory
 #ifdef SSD_TC2_PROFILE
     if (blockIdx.x == 0 && h == 0 && (l == 0 || l == 96) && status) {

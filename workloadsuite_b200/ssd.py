@@ -25,7 +25,7 @@ def _status_word(device) -> torch.Tensor:
     key = (device.type, device.index)
     st = _status.get(key)
     if st is None:
-        st = torch.zeros(128, dtype=torch.int32, device=device)
+        st = torch.zeros(1024, dtype=torch.int32, device=device)
         _status[key] = st
     return st
 
