@@ -210,12 +210,12 @@ def test_segmented_scan_equals_unsegmented(dtype):
 
 
 def test_chained_segments_tensor_core():
-    """Enough (batch, head-pair) units to fill the SMs: the segments of a sequence are chained inside one
-    launch (state handed over through scratch) instead of scanned twice."""
+    """At least one (batch, head-pair) sequence per SM: the tiles of all sequences are dealt out evenly over the
+    CTAs of one launch, and a sequence cut that way hands its state from CTA to CTA through scratch."""
     if not _tc_available():
         pytest.skip("tensor-core kernel not available")
     W = _ssd()
-    inp = O.make_inputs(b=30, s=1024, h=8, p=64, n=128, g=2, dtype=torch.bfloat16, init=True, seed=21,
+    inp = O.make_inputs(b=40, s=1024, h=8, p=64, n=128, g=2, dtype=torch.bfloat16, init=True, seed=21,
                         decay_scale=0.02)
     d = _to_dev(inp)
     assert W.plan(d["X"], d["A"], d["B"], d["C"], 256, nsegments=4)["launches"] == 1

@@ -70,8 +70,11 @@ struct Tc2Params {
   int upairs;   // batch * nheads / 2
 };
 
+// One work item: `ntiles` tiles of one (batch, head pair) sequence from token t_begin on.  in_slot / out_slot are
+// the scratch slots the state is taken from / handed to when the item is an inner piece of a sequence that
+// continues on a neighbouring CTA (-1: the sequence starts / ends here).
 struct Item {
-  int seg, bi, h0, gi, t_begin, ntiles;
+  int seg, bi, h0, gi, t_begin, ntiles, in_slot, out_slot;
 };
 
 __device__ __forceinline__ Item decode_item(const ScanParams& sp, int upairs, int item) {
@@ -85,6 +88,54 @@ __device__ __forceinline__ Item decode_item(const ScanParams& sp, int upairs, in
   it.t_begin = it.seg * sp.seg_len;
   const int t_end = min(sp.seqlen, it.t_begin + sp.seg_len);
   it.ntiles = (t_end - it.t_begin) / T;
+  it.in_slot = it.out_slot = -1;
+  return it;
+}
+
+// Work list of this CTA.
+//  - Regular mode: items blockIdx.x, blockIdx.x + gridDim.x, ... of the (segment, sequence) grid.
+//  - Chained mode (sp.chain): all tiles of all sequences, laid end to end, are cut into gridDim.x equal ranges,
+//    so every CTA gets the same number of tiles (+-1) whatever the number of sequences.  A range holds the
+//    tail of one sequence, whole sequences and the head of another; they are walked in reverse, head first:
+//    the head's state is what the next CTA's tail piece waits for, and a tail piece (walked last) then finds
+//    the state it needs already there when there is at least one sequence per CTA.
+struct Work {
+  int count;
+  int lo, hi, nt, pl;   // chained mode: global tile range, tiles per sequence, last sequence of the range
+};
+
+__device__ __forceinline__ Work work_list(const Tc2Params& prm) {
+  Work wk;
+  wk.lo = wk.hi = wk.pl = 0;
+  wk.nt = 1;
+  if (prm.sp.chain) {
+    wk.nt = prm.sp.seqlen / T;
+    const long long total = (long long)prm.upairs * wk.nt;
+    wk.lo = (int)((long long)blockIdx.x * total / gridDim.x);
+    wk.hi = (int)((long long)(blockIdx.x + 1) * total / gridDim.x);
+    wk.pl = wk.hi > wk.lo ? (wk.hi - 1) / wk.nt : 0;
+    wk.count = wk.hi > wk.lo ? wk.pl - wk.lo / wk.nt + 1 : 0;
+  } else {
+    wk.count = (int)blockIdx.x < prm.nitems ? (prm.nitems - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  }
+  return wk;
+}
+
+__device__ __forceinline__ Item work_item(const Tc2Params& prm, const Work& wk, int i) {
+  if (!prm.sp.chain) return decode_item(prm.sp, prm.upairs, blockIdx.x + i * gridDim.x);
+  const ScanParams& sp = prm.sp;
+  Item it;
+  const int u2 = wk.pl - i;
+  const int first = u2 * wk.nt, start = max(wk.lo, first), end = min(wk.hi, first + wk.nt);
+  const int hp = sp.nheads >> 1;
+  it.seg = 0;
+  it.bi = u2 / hp;
+  it.h0 = 2 * (u2 - it.bi * hp);
+  it.gi = it.h0 / (sp.nheads / sp.ngroups);
+  it.t_begin = (start - first) * T;
+  it.ntiles = end - start;
+  it.in_slot = start > first ? (int)blockIdx.x - 1 : -1;
+  it.out_slot = end < first + wk.nt ? (int)blockIdx.x : -1;
   return it;
 }
 
@@ -105,11 +156,20 @@ __device__ __forceinline__ bool wait2(uint64_t* bar, uint32_t parity, Misc2* m, 
 
 #ifdef SSD_TC2_TRACE
 // debug build: time stamps of pipeline events of CTA 0 for tiles [kTr0, kTr0+kTrN) into status[256...]
-constexpr int kTr0 = 20, kTrN = 6, kTrEv = 24;
+#ifndef SSD_TC2_TRACE_FIRST
+#define SSD_TC2_TRACE_FIRST 20
+#endif
+constexpr int kTr0 = SSD_TC2_TRACE_FIRST, kTrN = 6, kTrEv = 24;
 #define TRACE(ev, tile) { if (blockIdx.x == 0 && status && (int)(tile) >= kTr0 && (int)(tile) < kTr0 + kTrN) \
     status[256 + ((int)(tile) - kTr0) * kTrEv + (ev)] = (int)(clock64() & 0x7fffffff); }
 #else
 #define TRACE(ev, tile) {}
+#endif
+#ifdef SSD_TC2_TRACE
+#define ITRACE(idx) { if ((blockIdx.x == 0 || blockIdx.x == gridDim.x - 1) && status && (idx) < 32) \
+    status[128 + (blockIdx.x == 0 ? 0 : 32) + (idx)] = (int)(clock64() & 0x7fffffff); }
+#else
+#define ITRACE(idx) {}
 #endif
 
 template <typename T16, int N>
@@ -132,6 +192,10 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool want_y = sp.compute_y != 0;
   int32_t* status = sp.status;
+  if (tid == 0) ITRACE(0)
+#ifdef SSD_TC2_TRACE
+  if (tid == 0 && status) { unsigned long long g; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(g)); status[400 + blockIdx.x] = (int)(g & 0x7fffffff); }
+#endif
 
   if (tid == 0) {
     mbar_init(&m->full_b, 1); mbar_init(&m->full_c, 1);
@@ -169,8 +233,9 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       prefetch_tmap(&tmX); prefetch_tmap(&tmB); prefetch_tmap(&tmC); prefetch_tmap(&tmY);
       bool ok = true;
       uint32_t it = 0;   // running tile ordinal of this CTA
-      for (int item = blockIdx.x; item < prm.nitems && ok; item += gridDim.x) {
-        const Item w = decode_item(sp, prm.upairs, item);
+      const Work wk = work_list(prm);
+      for (int wi = 0; wi < wk.count && ok; ++wi) {
+        const Item w = work_item(prm, wk, wi);
         for (int j = 0; j < w.ntiles && ok; ++j, ++it) {
           const int t0 = w.t_begin + j * T;
           const uint32_t st = it % kXStages, use = it / kXStages;
@@ -218,8 +283,8 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         constexpr uint32_t idG = umma_idesc(128, 128, fmt, 0, 0);
         constexpr uint64_t dK = umma_desc_base(16, 1024);
         uint32_t ttot = 0;
-        for (int item = blockIdx.x; item < prm.nitems; item += gridDim.x)
-          ttot += decode_item(sp, prm.upairs, item).ntiles;
+        const Work wk = work_list(prm);
+        for (int wi = 0; wi < wk.count; ++wi) ttot += work_item(prm, wk, wi).ntiles;
         bool ok = true;
         for (uint32_t k = 0; k < ttot && ok; ++k) {
           // both heads are done reading G(k-1); B and C of tile k have landed
@@ -254,8 +319,9 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       const uint32_t tS = tb + 128, tY = tb + 256;
       bool ok = true;
       uint32_t k0 = 0;   // running tile ordinal of the item's first tile
-      for (int item = blockIdx.x; item < prm.nitems && ok; item += gridDim.x) {
-        const int nt = decode_item(sp, prm.upairs, item).ntiles;
+      const Work wk = work_list(prm);
+      for (int wi = 0; wi < wk.count && ok; ++wi) {
+        const int nt = work_item(prm, wk, wi).ntiles;
 #pragma unroll 1
         for (int j = 0; j < nt && ok; ++j) {
           const uint32_t k = k0 + j;
@@ -297,8 +363,8 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         constexpr uint32_t idKM = umma_idesc(128, 64, fmt, 0, 1);
         constexpr uint64_t dMN = umma_desc_base(kBlk, 1024);
         uint32_t ttot = 0;
-        for (int item = blockIdx.x; item < prm.nitems; item += gridDim.x)
-          ttot += decode_item(sp, prm.upairs, item).ntiles;
+        const Work wk = work_list(prm);
+        for (int wi = 0; wi < wk.count; ++wi) ttot += work_item(prm, wk, wi).ntiles;
         bool ok = true;
 #pragma unroll 1
         for (uint32_t k = 0; k < ttot && ok; ++k) {
@@ -363,7 +429,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     float asum = 0.f, acomp = 0.f;   // compensated (Kahan) sum of the tile totals; FP64 is slow on this part
 
     // prefix sum of the log-decay over the 128 rows (model_ref.py:135); publishes cs*log2(e) for the P step
-    auto scan_tile = [&](float a, uint32_t par, float& cs_o, float& tot_o, float& cs2_o) {
+    auto scan_tile = [&](float a, uint32_t par, bool sync_after, float& cs_o, float& tot_o, float& cs2_o) {
       float v = a;
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {
@@ -381,7 +447,9 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       // column factor of the factored decay mask: exp(cs at the end of this row's 32-token block - cs_row)
       m->cf[h][par][l] = ex2(__shfl_sync(0xffffffffu, cs2_o, 31) - cs2_o);
       if (lane == 31) m->cend[h][par][q] = cs2_o;
-      named_bar_sync(bar_id, 128);
+      // cf / cend are read one tile later and the warp sums are rewritten one tile later: the barrier of the Y
+      // read-out lies in between, except after an item's first tile and in state-only mode
+      if (sync_after) named_bar_sync(bar_id, 128);
       PROF(13)
     };
     // Xd = exp(cs_last - cs_l) * x~ (model_ref.py:144,148) from X stage `st` into this head's Xd buffer
@@ -483,9 +551,11 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       return true;
     };
 
-    for (int item = blockIdx.x; item < prm.nitems && ok; item += gridDim.x) {
-      const Item w = decode_item(sp, prm.upairs, item);
+    const Work wk = work_list(prm);
+    for (int wi = 0; wi < wk.count && ok; ++wi) {
+      const Item w = work_item(prm, wk, wi);
       if (w.ntiles == 0) continue;
+      if (h == 0 && l == 96) ITRACE(1 + wi)
       const int hi = w.h0 + h;
       const int64_t unit = (int64_t)w.bi * sp.nheads + hi;
       const float* Ag = sp.A + w.bi * sp.as[0] + hi * sp.as[2];
@@ -539,9 +609,9 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         // ---- state leaving the item: it is final once the last tile's update (step a) is done, so it is
         //      handed over here, ahead of the rest of that tile; the next item's first log-decays are fetched too
         if (j >= 0 && !have_next) {
-          const bool hand_over = sp.chain && (w.seg + 1 < sp.nseg);
+          const bool hand_over = w.out_slot >= 0;
           if (hand_over) {
-            const int64_t slot = unit * sp.nseg + w.seg;
+            const int64_t slot = 2 * w.out_slot + h;
             if (owns_state) {
               float4* F = reinterpret_cast<float4*>(sp.chain_state + slot * (int64_t)(N * P) + (int64_t)l * P);
     #pragma unroll
@@ -567,9 +637,8 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             if (sp.fin_ld && l == 0)
               sp.fin_ld[unit * sp.finld_unit_stride + fseg * sp.finld_seg_stride] = asum0 + asum;
           }
-              const int nitem = item + gridDim.x;
-          if (nitem < prm.nitems) {
-            const Item wn = decode_item(sp, prm.upairs, nitem);
+          if (wi + 1 < wk.count) {
+            const Item wn = work_item(prm, wk, wi + 1);
             if (wn.ntiles > 0) {
               const int hn = wn.h0 + h;
               a_next = sp.A[wn.bi * sp.as[0] + hn * sp.as[2] + (int64_t)(wn.t_begin + l) * sp.as[1]];
@@ -593,7 +662,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             a_next = Ag[(int64_t)(t0 + 2 * T + l) * sp.as[1]];
             if (Dg) dt_next = Cvt<T16>::to_f(Dg[(int64_t)(t0 + 2 * T + l) * sp.dts[1]]);
           }
-          scan_tile(a, itn & 1, cs_n, tot_n, cs2_n);
+          scan_tile(a, itn & 1, j < 0 || !want_y, cs_n, tot_n, cs2_n);
           if (h == 0 && l == 96) TRACE(18, itn)
           ok = cwait(&m->full_x[h][itn % kXStages], (itn / kXStages) & 1, STATUS_WAIT_TIMEOUT_TMA);
           if (!ok) break;
@@ -610,9 +679,9 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         // ---- state entering the item (after the first tile's Xd is on its way to the S MMA: the wait for a
         //      chained predecessor and the state load then overlap that MMA)
         if (j == -1) {
-          if (sp.chain && w.seg > 0) {
+          if (w.in_slot >= 0) {
             // wait (bounded) for the previous segment of this unit, which another CTA may still be finishing
-            const int64_t slot = unit * sp.nseg + (w.seg - 1);
+            const int64_t slot = 2 * w.in_slot + h;
             if (l == 0) {
               const long long c0 = clock64();
               while (true) {
@@ -770,6 +839,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 
     }
     if (ok && y_pending) ok = finish_y();
+    if (h == 0 && l == 96) ITRACE(30)
     if (l == 0 && store_pending) bulk_wait_all();   // the last Y tile must have left shared memory
 #ifdef SSD_TC2_PROFILE
     if (blockIdx.x == 0 && h == 0 && (l == 0 || l == 96) && status) {
@@ -781,6 +851,9 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   // ---------------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
+#ifdef SSD_TC2_TRACE
+  if (tid == 0 && status) { unsigned long long g; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(g)); status[560 + blockIdx.x] = (int)(g & 0x7fffffff); }
+#endif
   if (warp == 0) {
     __syncwarp();
     tmem_dealloc(tb, 512);
@@ -794,7 +867,9 @@ int launch_typed2(const CUtensorMap& tx, const CUtensorMap& tb, const CUtensorMa
   constexpr int smem = Layout2<N>::kBytes;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
     return SSD_ERR_CUDA;
-  const int grid = std::min(prm.nitems, kSms);
+  // chained mode: the tiles of all sequences are dealt out evenly, every CTA gets at least one
+  const long long tiles = (long long)prm.upairs * (prm.sp.seqlen / T);
+  const int grid = prm.sp.chain ? (int)std::min<long long>(tiles, kSms) : std::min(prm.nitems, kSms);
   kern<<<grid, kThreads2, smem, stream>>>(tx, tb, tc, ty, prm);
   return cudaGetLastError() == cudaSuccess ? SSD_OK : SSD_ERR_CUDA;
 }
@@ -813,25 +888,21 @@ static double round_efficiency(int64_t items) {
   return (double)items / (double)(rounds * kSms);
 }
 
-// With at least about one item per SM the segments of a sequence are chained inside one launch (each
-// starts from the state its predecessor left in scratch): that only serves to even out the last round.
-// With fewer sequences than SMs the segments must run concurrently instead: two passes and a fold.
+// With at least one sequence per SM the tiles of all sequences are dealt out evenly over the CTAs inside one
+// launch; a sequence cut that way hands its state from CTA to CTA through scratch ("chained").  With fewer
+// sequences than SMs the cuts must be scanned concurrently instead: two passes and a fold.
 bool tc2_chain_segments(const SsdArgs& a, int nseg) {
   const int64_t upairs = (int64_t)a.batch * a.nheads / 2;
-  return nseg > 1 && upairs >= 120;
+  return nseg > 1 && upairs >= kSms;
 }
 
 int tc2_default_segments(const SsdArgs& a) {
   const int64_t upairs = (int64_t)a.batch * a.nheads / 2;
   const int tiles = a.seqlen / T;
-  if (upairs >= 120) {
-    int best = 1;
-    for (int nseg = 1; nseg <= 16 && tiles / nseg >= 4; nseg *= 2) {
-      best = nseg;
-      if (round_efficiency(upairs * nseg) >= 0.85) break;
-    }
-    return best;
-  }
+  // whole sequences already fill the rounds of the persistent grid well: no cuts; else the even deal (any count
+  // above one selects it, the cut points follow from the grid)
+  if (upairs >= kSms) return (round_efficiency(upairs) >= 0.97 || tiles < 2) ? 1 : 2;
+  if (upairs >= 120) return 1;
   // Fewer sequences than SMs: cutting them into concurrently scanned segments costs a second pass
   // (about 0.4 of a full pass) and a per-item start-up (about 1.5 tile times).  Pick the count that
   // minimises the modelled time, in tile times, of the busiest CTA.
