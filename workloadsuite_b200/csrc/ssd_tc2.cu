@@ -1,20 +1,26 @@
 // Two-head tensor-core SSD forward for sm_100a (the fast path when the heads of a
-// group come in pairs).  One persistent CTA per SM walks (batch, head pair, segment)
-// items; inside an item it walks the 128-token tiles in order.
+// group come in pairs).  One persistent CTA per SM walks work items (a run of
+// 128-token tiles of one (batch, head pair) sequence) in order.
 //
 // The two heads of a pair read the same B and C (model_ref.py:97-99), so B, C and
-// G = C.B^T (model_ref.py:143) are loaded/computed once per tile and shared; each head
-// has its own compute warpgroup (one thread per tile row / TMEM lane) and its own
-// TMEM accumulators.  Per head and tile, in the order the warpgroup runs them:
-//   a. H <- exp(cs_last) H + S           (model_ref.py:150,156)   S = B^T.Xd from the previous step c
-//   b. Y <- exp(cs_l) * (C.H)            (model_ref.py:160-161)   scaled in place in TMEM, H copy -> smem
-//   c. next tile: prefix sum (:135), Xd = exp(cs_last - cs_l) x~ (:144,148) -> smem -> S MMA
-//   d. P = G o exp(segsum) o causal      (:139-145) -> TMEM as the A operand of Y += P.X
-//   e. Y -> global                        (:162)
-// Warp 0 is the TMA producer, warp 1 issues the shared G MMAs, warps 2 and 3 issue the
-// per-head MMAs (one thread each, blocking on the mbarriers in the order its head's
-// warpgroup raises them, so the two heads may drift apart), warps 4-7 and 8-11 are
-// the compute warpgroups.  All waits are bounded.
+// G = C.B^T (model_ref.py:143) are loaded/computed once per tile and shared.  The two
+// heads' Xd tiles and 16-bit state copies lie one 64-column block apart in shared
+// memory, so S = B^T.[Xd0|Xd1] and C.[H0|H1] are single N = 128 MMAs as well (an N = 64
+// MMA occupies the tensor pipe as long as an N = 128 one).  Each head has its own
+// compute warpgroup (one thread per tile row / TMEM lane).  Per head and tile k, in
+// the order the warpgroup runs them inside one loop iteration:
+//   a. H <- exp(cs_last) H + S(k)         (model_ref.py:150,156)   S = B^T.Xd from step c of the previous iteration
+//   e. Y(k-1) -> global                    (:162)                   the P.X MMA of tile k-1 ran under step a
+//   c. tile k+1: prefix sum (:135), Xd = exp(cs_last - cs_l) x~ (:144,148) -> smem -> S MMA
+//   d. P(k) = G o exp(segsum) o causal     (:139-145) -> TMEM as the A operand of Y += P.X
+//   b. Y(k) <- exp(cs_l) * (C.H)           (:160-161) scaled in place in TMEM (the C.H MMA ran under steps c, d)
+//      16-bit copy of H(k+1) -> smem for the next C.H MMA
+// Warp 0 is the TMA producer, warp 1 issues the G MMAs, warp 2 the S and C.H MMAs,
+// warp 3 the two heads' P.X MMAs (one thread each, blocking on the mbarriers in the
+// order the warpgroups raise them); warps 4-7 and 8-11 are the compute warpgroups.
+// tcgen05.mma holds its issuing thread for about as long as the MMA runs (77-160
+// cycles per 128xNx16 step, depending on the operand layouts), which is why the three
+// MMA streams have a thread each.  All waits are bounded.
 #include <cuda.h>
 
 #include <algorithm>
