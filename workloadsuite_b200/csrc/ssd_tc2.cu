@@ -52,7 +52,22 @@ struct Layout2 {
   static constexpr int kBytes = oMisc + 2560;   // no slack: the dynamic segment must start 1024-byte aligned
 };
 
+// Work list of this CTA.
+//  - Regular mode: items blockIdx.x, blockIdx.x + gridDim.x, ... of the (segment, sequence) grid.
+//  - Chained mode (sp.chain): all tiles of all sequences, laid end to end, are cut into gridDim.x equal ranges,
+//    so every CTA gets the same number of tiles (+-1) whatever the number of sequences.  A range holds the
+//    tail of one sequence, whole sequences and the head of another; they are walked in reverse, head first:
+//    the head's state is what the next CTA's tail piece waits for, and a tail piece (walked last) then finds
+//    the state it needs already there when there is at least one sequence per CTA.
+// Computed once per CTA (thread 0, into shared memory): the 64-bit divisions are bulky code.
+struct Work {
+  int count;
+  int lo, hi, nt, pl;   // chained mode: global tile range, tiles per sequence, last sequence of the range
+  int hp, hpg;          // head pairs per batch entry, heads per B/C group
+};
+
 struct Misc2 {
+  Work work;
   uint64_t full_b, full_c, empty_b, empty_c;
   uint64_t full_x[2][kXStages], empty_x[2][kXStages];
   uint64_t bar_g;
@@ -83,37 +98,12 @@ struct Item {
   int seg, bi, h0, gi, t_begin, ntiles, in_slot, out_slot;
 };
 
-__device__ __forceinline__ Item decode_item(const ScanParams& sp, int upairs, int item) {
-  Item it;
-  it.seg = item / upairs;
-  const int u2 = item - it.seg * upairs;
-  const int hp = sp.nheads >> 1;
-  it.bi = u2 / hp;
-  it.h0 = 2 * (u2 - it.bi * hp);
-  it.gi = it.h0 / (sp.nheads / sp.ngroups);
-  it.t_begin = it.seg * sp.seg_len;
-  const int t_end = min(sp.seqlen, it.t_begin + sp.seg_len);
-  it.ntiles = (t_end - it.t_begin) / T;
-  it.in_slot = it.out_slot = -1;
-  return it;
-}
-
-// Work list of this CTA.
-//  - Regular mode: items blockIdx.x, blockIdx.x + gridDim.x, ... of the (segment, sequence) grid.
-//  - Chained mode (sp.chain): all tiles of all sequences, laid end to end, are cut into gridDim.x equal ranges,
-//    so every CTA gets the same number of tiles (+-1) whatever the number of sequences.  A range holds the
-//    tail of one sequence, whole sequences and the head of another; they are walked in reverse, head first:
-//    the head's state is what the next CTA's tail piece waits for, and a tail piece (walked last) then finds
-//    the state it needs already there when there is at least one sequence per CTA.
-struct Work {
-  int count;
-  int lo, hi, nt, pl;   // chained mode: global tile range, tiles per sequence, last sequence of the range
-};
-
-__device__ __forceinline__ Work work_list(const Tc2Params& prm) {
+__device__ __forceinline__ void work_list(const Tc2Params& prm, Work* out) {
   Work wk;
   wk.lo = wk.hi = wk.pl = 0;
   wk.nt = 1;
+  wk.hp = prm.sp.nheads >> 1;
+  wk.hpg = prm.sp.nheads / prm.sp.ngroups;
   if (prm.sp.chain) {
     wk.nt = prm.sp.seqlen / T;
     const long long total = (long long)prm.upairs * wk.nt;
@@ -124,28 +114,36 @@ __device__ __forceinline__ Work work_list(const Tc2Params& prm) {
   } else {
     wk.count = (int)blockIdx.x < prm.nitems ? (prm.nitems - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
   }
-  return wk;
+  *out = wk;
 }
 
 __device__ __forceinline__ Item work_item(const Tc2Params& prm, const Work& wk, int i) {
-  if (!prm.sp.chain) return decode_item(prm.sp, prm.upairs, blockIdx.x + i * gridDim.x);
   const ScanParams& sp = prm.sp;
   Item it;
-  const int u2 = wk.pl - i;
-  const int first = u2 * wk.nt, start = max(wk.lo, first), end = min(wk.hi, first + wk.nt);
-  const int hp = sp.nheads >> 1;
-  it.seg = 0;
-  it.bi = u2 / hp;
-  it.h0 = 2 * (u2 - it.bi * hp);
-  it.gi = it.h0 / (sp.nheads / sp.ngroups);
-  it.t_begin = (start - first) * T;
-  it.ntiles = end - start;
-  it.in_slot = start > first ? (int)blockIdx.x - 1 : -1;
-  it.out_slot = end < first + wk.nt ? (int)blockIdx.x : -1;
+  int u2;
+  if (sp.chain) {
+    u2 = wk.pl - i;
+    const int first = u2 * wk.nt, start = max(wk.lo, first), end = min(wk.hi, first + wk.nt);
+    it.seg = 0;
+    it.t_begin = (start - first) * T;
+    it.ntiles = end - start;
+    it.in_slot = start > first ? (int)blockIdx.x - 1 : -1;
+    it.out_slot = end < first + wk.nt ? (int)blockIdx.x : -1;
+  } else {
+    const int item = blockIdx.x + i * gridDim.x;
+    it.seg = item / prm.upairs;
+    u2 = item - it.seg * prm.upairs;
+    it.t_begin = it.seg * sp.seg_len;
+    it.ntiles = (min(sp.seqlen, it.t_begin + sp.seg_len) - it.t_begin) / T;
+    it.in_slot = it.out_slot = -1;
+  }
+  it.bi = u2 / wk.hp;
+  it.h0 = 2 * (u2 - it.bi * wk.hp);
+  it.gi = it.h0 / wk.hpg;
   return it;
 }
 
-// Deliberately not inlined: the kernel's steady-state loop has to stay small enough for the instruction cache.
+// Bounded wait on an mbarrier phase; false when it gave up (or another role already had).
 __device__ __forceinline__ bool wait2(uint64_t* bar, uint32_t parity, Misc2* m, int code, int32_t* status) {
   if (mbar_try_wait(bar, parity)) return true;   // the common case in steady state: no clock read, no sleep
   const long long t0 = clock64();
@@ -221,6 +219,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       mbar_init(&m->bar_p[h], 4);   // one arrival per compute warp (lane 0, after a warp barrier)
     }
     m->abort_flag = 0;
+    work_list(prm, &m->work);
     fence_mbar_init();
   }
   if (warp == 0) tmem_alloc(&m->tmem_base, 512);
@@ -239,7 +238,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       prefetch_tmap(&tmX); prefetch_tmap(&tmB); prefetch_tmap(&tmC); prefetch_tmap(&tmY);
       bool ok = true;
       uint32_t it = 0;   // running tile ordinal of this CTA
-      const Work wk = work_list(prm);
+      const Work wk = m->work;
       for (int wi = 0; wi < wk.count && ok; ++wi) {
         const Item w = work_item(prm, wk, wi);
         for (int j = 0; j < w.ntiles && ok; ++j, ++it) {
@@ -289,7 +288,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         constexpr uint32_t idG = umma_idesc(128, 128, fmt, 0, 0);
         constexpr uint64_t dK = umma_desc_base(16, 1024);
         uint32_t ttot = 0;
-        const Work wk = work_list(prm);
+        const Work wk = m->work;
         for (int wi = 0; wi < wk.count; ++wi) ttot += work_item(prm, wk, wi).ntiles;
         bool ok = true;
         for (uint32_t k = 0; k < ttot && ok; ++k) {
@@ -325,7 +324,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       const uint32_t tS = tb + 128, tY = tb + 256;
       bool ok = true;
       uint32_t k0 = 0;   // running tile ordinal of the item's first tile
-      const Work wk = work_list(prm);
+      const Work wk = m->work;
       for (int wi = 0; wi < wk.count && ok; ++wi) {
         const int nt = work_item(prm, wk, wi).ntiles;
 #pragma unroll 1
@@ -369,7 +368,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         constexpr uint32_t idKM = umma_idesc(128, 64, fmt, 0, 1);
         constexpr uint64_t dMN = umma_desc_base(kBlk, 1024);
         uint32_t ttot = 0;
-        const Work wk = work_list(prm);
+        const Work wk = m->work;
         for (int wi = 0; wi < wk.count; ++wi) ttot += work_item(prm, wk, wi).ntiles;
         bool ok = true;
 #pragma unroll 1
@@ -557,7 +556,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       return true;
     };
 
-    const Work wk = work_list(prm);
+    const Work wk = m->work;
     for (int wi = 0; wi < wk.count && ok; ++wi) {
       const Item w = work_item(prm, wk, wi);
       if (w.ntiles == 0) continue;
