@@ -75,7 +75,7 @@ struct Misc2 {
   uint64_t bar_xd, bar_h, bar_e;      // one arrival per compute warp of either head (8)
   uint64_t bar_p[2];                  // one arrival per compute warp of the head (4)
   uint32_t tmem_base;
-  volatile int abort_flag;
+  volatile int abort_flag;   // 0, or the status code of the first wait that gave up (every role then leaves)
   float wsum[2][4];
   // Double-buffered by tile parity: step c writes the next tile's values while step d still reads this tile's.
   alignas(16) float cf[2][2][T];   // [head][parity][row]: exp(cs at the end of the row's 32-block - cs of the row)
@@ -150,8 +150,7 @@ __device__ __forceinline__ bool wait2(uint64_t* bar, uint32_t parity, Misc2* m, 
   while (!mbar_try_wait_sleep(bar, parity, 200000u)) {
     if (m->abort_flag) return false;
     if (clock64() - t0 > kWaitClocks) {
-      m->abort_flag = 1;
-      if (status) atomicCAS(status, 0, code);
+      m->abort_flag = code;   // reported to the caller's status word at kernel end
       return false;
     }
   }
@@ -695,8 +694,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 if (f >= 4) break;   // all four warps of the predecessor's warpgroup have published
                 if (m->abort_flag) break;
                 if (clock64() - c0 > kWaitClocks) {
-                  m->abort_flag = 1;
-                  if (status) atomicCAS(status, 0, (int)STATUS_WAIT_TIMEOUT_CHAIN);
+                  m->abort_flag = (int)STATUS_WAIT_TIMEOUT_CHAIN;
                   break;
                 }
               }
@@ -856,6 +854,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   // ---------------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
+  if (tid == 0 && m->abort_flag && status) atomicCAS(status, 0, (int)m->abort_flag);
 #ifdef SSD_TC2_TRACE
   if (tid == 0 && status) { unsigned long long g; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(g)); status[560 + blockIdx.x] = (int)(g & 0x7fffffff); }
 #endif
