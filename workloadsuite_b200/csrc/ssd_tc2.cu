@@ -752,14 +752,21 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
               uint32_t gd[32];
               tmem_ld32(tG + tlane + 32 * q, gd);
               tmem_ld_wait();
+              // One ex2 per four columns: exp(cs_l - cs_{s+1}) = exp(cs_l - cs_s) * exp(-a_{s+1}), the per-token
+              // factor exp(-a) coming from the lane that owns the row (clamped: an entry above the diagonal may
+              // overflow, it is masked out by a select, never multiplied into anything that is kept).
+              const float einv = ex2(fminf(__shfl_up_sync(0xffffffffu, cs2, 1) - cs2, 126.f));
               uint32_t pk[16];
 #pragma unroll
-              for (int e2 = 0; e2 < 16; ++e2) {
-                // cs of the two columns comes from the lanes that own those rows
-                const float c0 = __shfl_sync(0xffffffffu, cs2, 2 * e2), c1 = __shfl_sync(0xffffffffu, cs2, 2 * e2 + 1);
-                const float v0 = __uint_as_float(gd[2 * e2]) * ex2(cs2 - c0);
-                const float v1 = __uint_as_float(gd[2 * e2 + 1]) * ex2(cs2 - c1);
-                pk[e2] = pack2<T16>(2 * e2 <= lane ? v0 : 0.f, 2 * e2 + 1 <= lane ? v1 : 0.f);
+              for (int e4 = 0; e4 < 8; ++e4) {
+                const float c0 = __shfl_sync(0xffffffffu, cs2, 4 * e4);   // cs of the column: from the lane owning that row
+                const float f1 = __shfl_sync(0xffffffffu, einv, 4 * e4 + 1), f2 = __shfl_sync(0xffffffffu, einv, 4 * e4 + 2);
+                const float f3 = __shfl_sync(0xffffffffu, einv, 4 * e4 + 3);
+                const float w0 = ex2(cs2 - c0), w1 = w0 * f1, w2 = w1 * f2, w3 = w2 * f3;
+                const float v0 = __uint_as_float(gd[4 * e4]) * w0, v1 = __uint_as_float(gd[4 * e4 + 1]) * w1;
+                const float v2 = __uint_as_float(gd[4 * e4 + 2]) * w2, v3 = __uint_as_float(gd[4 * e4 + 3]) * w3;
+                pk[2 * e4] = pack2<T16>(4 * e4 <= lane ? v0 : 0.f, 4 * e4 + 1 <= lane ? v1 : 0.f);
+                pk[2 * e4 + 1] = pack2<T16>(4 * e4 + 2 <= lane ? v2 : 0.f, 4 * e4 + 3 <= lane ? v3 : 0.f);
               }
               tmem_st16(tP + tlane + 16 * q, pk);
             }
