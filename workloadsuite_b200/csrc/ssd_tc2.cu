@@ -147,7 +147,7 @@ __device__ __forceinline__ Item work_item(const Tc2Params& prm, const Work& wk, 
 __device__ __forceinline__ bool wait2(uint64_t* bar, uint32_t parity, Misc2* m, int code, int32_t* status) {
   if (mbar_try_wait(bar, parity)) return true;   // the common case in steady state: no clock read, no sleep
   const long long t0 = clock64();
-  while (!mbar_try_wait_sleep(bar, parity, 200000u)) {
+  while (!mbar_try_wait(bar, parity)) {   // (try_wait parks the thread for a short, hardware-chosen time by itself)
     if (m->abort_flag) return false;
     if (clock64() - t0 > kWaitClocks) {
       m->abort_flag = code;   // reported to the caller's status word at kernel end
