@@ -49,6 +49,11 @@ WORKLOAD_NAMES = {
 TDT = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
 L2_BYTES = 126e6
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu capture summarised
+# in profiles/ssd_tc2_kernel_cfg2.md (same command line as this bench, --steps 2 --warmup 3); None where no capture
+# of that (workload, kernel, world size) exists.
+NCU_TRAFFIC_BYTES = {("cfg2", "tcgen05", 1): 666.3e6}
+
 
 def algorithmic_bytes(cfg, h=None, s=None):
     """X read + Y write + B + C + fp32 log-decay (+ fp32 initial states), per step."""
@@ -444,7 +449,8 @@ def main():
                        "kernel": kname, "launch": launch_mode, "segments_per_sequence": plan["nsegments"],
                        "kernel_launches_per_step": launches_per_step[0]},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_kind": peak_kind, "frac_of_8TBs": achieved / 8000.0, "traffic": None,
+                         "peak_kind": peak_kind, "frac_of_8TBs": achieved / 8000.0,
+                         "traffic": NCU_TRAFFIC_BYTES.get((args.workload, kname, world)),
                          "algorithmic_bytes_per_step_per_gpu": set_bytes, "algorithmic_bytes_whole_job": total_bytes},
             "cpu_baseline": cpu_baseline,
             "e2e": e2e,
