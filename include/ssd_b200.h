@@ -94,6 +94,12 @@ typedef struct SsdArgs {
   int64_t c_stride[3];          /* b, s, g */
   int64_t dt_stride[3];         /* b, s, h */
   int64_t y_stride[3];          /* b, s, h */
+  /* Optional fused epilogue of SSDLayer.forward after the core (model_ref.py:116-118):
+   *   Y <- (Y + x * D[head]) * silu(z)
+   * with x the X input, evaluated in fp32 and rounded once.  D == NULL skips the skip term, Z == NULL the gate. */
+  const float* D;               /* [h]        fp32, or NULL            model_ref.py:116 */
+  const void*  Z;               /* [b,s,h,p]  dtype, or NULL           model_ref.py:118 */
+  int64_t z_stride[3];          /* b, s, h */
 } SsdArgs;
 
 /* Library/ABI version (bumped when SsdArgs changes). */
@@ -121,7 +127,9 @@ int ssd_b200_plan(const SsdArgs* args, int32_t* kernel, int32_t* nsegments, int3
 /* The SSD forward: replaces SSDLayer._ssd_core, model_ref.py:123-162
  * (in-chunk prefix sum :135, decay mask :139-141, C.B^T :143, Y_diag :145,
  * chunk states :148-150, inter-chunk recurrence :152-157, Y_off :160-161,
- * sum :162), plus the GQA broadcast of :97-99 and the X*dt product of :144. */
+ * sum :162), plus the GQA broadcast of :97-99, the X*dt product of :144 and,
+ * when D / Z are given, the skip and gate of :116-118 applied to Y before it is
+ * written. */
 int ssd_b200_forward(const SsdArgs* args, void* stream);
 
 /* Fold per-shard results of a sequence-sharded scan into the state entering one

@@ -211,6 +211,21 @@ def ssd_layer_pre(layer, u: torch.Tensor):
     return x, z, B, C, dt, A_dt
 
 
+def ssd_epilogue(Y: torch.Tensor, x: torch.Tensor, D=None, z=None, dtype=None) -> torch.Tensor:
+    """Skip and gate of ``SSDLayer.forward`` after the core (``model_ref.py:116-118``), without the projection:
+    ``(Y + x * D[head]) * silu(z)`` on [b,s,h,p] tensors, each step cast to ``dtype`` as the reference does
+    (default: the dtype of Y); pass ``torch.float64`` for an exact reference."""
+    import torch.nn.functional as F
+
+    dtype = dtype or Y.dtype
+    out = Y.to(dtype)
+    if D is not None:
+        out = out + x.to(dtype) * D.to(dtype).view(1, 1, -1, 1)                # :116
+    if z is not None:
+        out = out * F.silu(z.to(dtype))                                      # :118
+    return out
+
+
 def ssd_layer_post(layer, Y: torch.Tensor, x: torch.Tensor, z: torch.Tensor) -> torch.Tensor:
     """``SSDLayer.forward`` after the core call (``model_ref.py:116-119``)."""
     import torch.nn.functional as F

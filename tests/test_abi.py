@@ -26,8 +26,8 @@ def test_header_symbols_all_exported(lib):
 
 
 def test_struct_layout_matches_header():
-    # 12 pointer/size_t fields, 12 int32, 6 x 3 int64
-    assert C.sizeof(_lib.SsdArgs) == 12 * 8 + 12 * 4 + 18 * 8
+    # 14 pointer/size_t fields, 12 int32, 7 x 3 int64
+    assert C.sizeof(_lib.SsdArgs) == 14 * 8 + 12 * 4 + 21 * 8
     assert _lib.SsdArgs.batch.offset == 96
     assert _lib.SsdArgs.x_stride.offset == 144
 

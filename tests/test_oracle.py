@@ -91,3 +91,26 @@ def test_sequence_shard_fold_reproduces_unsharded_state():
         assert O.error_metrics(Yr, Yfull[:, sl])[0] < 1e-12
     Hend = O.fold_incoming_state(finals, lds, R, initial=inp["initial_states"])
     assert (Hend - Hfull).abs().max() / Hfull.abs().max() < 1e-12
+
+
+def test_layer_oracle_reproduces_reference_model_output(golden_dir):
+    """``ssd_layer_pre`` -> ``ssd_chunked`` -> ``ssd_epilogue`` -> ``out_proj`` (the oracle's restatement of
+    ``SSDLayer.forward``, ``model_ref.py:68-121``) against the output the unmodified reference model produced
+    for the same weights and input (fixture written by tests/golden/make_golden.py)."""
+    from workloadsuite_b200 import mamba_model as M
+
+    z = np.load(golden_dir / "model_tiny.npz")
+    model = M.Model(*[int(v) for v in z["__init"]]).eval()
+    model.load_state_dict({k: torch.from_numpy(z[k]) for k in z.files if not k.startswith("__")}, strict=True)
+    u = torch.from_numpy(z["__input"])
+    with torch.inference_mode():
+        for layer in model.layers:
+            x, zz, B, C, dt, A_dt = O.ssd_layer_pre(layer, u)
+            Y = O.ssd_chunked(x, A_dt, B, C, layer.block_len, dt=dt)
+            Y = O.ssd_epilogue(Y, x, layer.D, zz.reshape(Y.shape))
+            u = u + layer.out_proj(Y.reshape(u.shape[0], u.shape[1], -1))
+        out = model.final_norm(u)
+    ref = torch.from_numpy(z["__output"])
+    assert out.dtype == ref.dtype
+    err = (out.double() - ref.double()).abs().max().item() / ref.double().abs().max().item()
+    assert err < 2e-3, err   # same operations in the same precision; only kernel-level summation order may differ

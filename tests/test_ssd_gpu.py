@@ -330,6 +330,51 @@ def test_full_size_properties(name):
 
 # ---------------------------------------------------------------- host-buffer entry point and the drop-in Model
 
+@pytest.mark.parametrize("case", ["pairs_bf16", "pairs_fp16_dt_segmented", "chained_bf16_dt", "single_heads_fp16", "fp32_simt",
+                                  "skip_only", "gate_only"])
+def test_skip_and_gate_epilogue(case):
+    """``Y <- (Y + X * D) * silu(z)`` (``model_ref.py:116-118``) applied by the kernels: fused in the two-head
+    tensor-core kernel, a kernel of its own behind the others.  Reference: fp64 recurrence + fp64 epilogue."""
+    W = _ssd()
+    kw = dict(p=64, n=128, g=1, init=False, decay_scale=0.05)
+    nseg, kernel, use_dt, use_D, use_z = None, None, False, True, True
+    if case == "pairs_bf16":
+        shape = dict(b=2, s=512, h=4, dtype=torch.bfloat16, seed=41)
+    elif case == "pairs_fp16_dt_segmented":
+        shape, nseg, use_dt = dict(b=1, s=1024, h=4, dtype=torch.float16, seed=42), 4, True
+    elif case == "chained_bf16_dt":
+        shape, nseg, use_dt = dict(b=40, s=512, h=8, dtype=torch.bfloat16, seed=43), 2, True
+        kw["g"] = 2
+    elif case == "single_heads_fp16":
+        shape = dict(b=2, s=256, h=3, dtype=torch.float16, seed=44)
+        kw["g"] = 3
+    elif case == "fp32_simt":
+        shape, kernel = dict(b=2, s=256, h=4, dtype=torch.float32, seed=45), "scan_f32"
+        kw["n"] = 16
+    elif case == "skip_only":
+        shape, use_z = dict(b=1, s=256, h=2, dtype=torch.bfloat16, seed=46), False
+    else:
+        shape, use_D = dict(b=1, s=256, h=2, dtype=torch.bfloat16, seed=47), False
+    dtype = shape["dtype"]
+    if dtype != torch.float32 and kernel is None and not _tc_available():
+        pytest.skip("tensor-core kernel not available")
+    inp = O.make_inputs(**shape, **kw)
+    gen = torch.Generator().manual_seed(shape["seed"] + 100)
+    b, s, h, p = inp["X"].shape
+    D = torch.randn(h, generator=gen) if use_D else None
+    z = torch.randn(b, s, h, p, generator=gen).to(dtype) if use_z else None
+    dt = (0.05 + torch.rand(b, s, h, generator=gen)).to(dtype) if use_dt else None
+    d = _to_dev(inp)
+    Y = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], 128, dt=None if dt is None else dt.to(DEV), kernel=kernel,
+                      nsegments=nseg, D=None if D is None else D.to(DEV), z=None if z is None else z.to(DEV))
+    torch.cuda.synchronize()
+    Yr = O.ssd_recurrence(inp["X"], inp["A"], inp["B"], inp["C"], dt=dt)
+    Yr = O.ssd_epilogue(Yr.double(), inp["X"].double(), None if D is None else D.double(),
+                        None if z is None else z.double(), dtype=torch.float64)
+    per_bh, fro = O.error_metrics(Y.cpu(), Yr)
+    assert per_bh < TOL[dtype] and fro < TOL[dtype], (case, per_bh, fro)
+
+
 def test_host_buffer_forward_equals_device_forward():
     W = _ssd()
     inp = O.make_inputs(b=3, s=512, h=8, p=64, n=64, g=2, dtype=torch.bfloat16, init=True, seed=13, decay_scale=0.1)

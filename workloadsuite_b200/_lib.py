@@ -11,7 +11,7 @@ from pathlib import Path
 
 from . import build as _build
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 SSD_OK = 0
 ERRORS = {
@@ -44,6 +44,7 @@ class SsdArgs(C.Structure):
         ("kernel", C.c_int32), ("flags", C.c_int32), ("nsegments", C.c_int32), ("reserved0", C.c_int32),
         ("x_stride", C.c_int64 * 3), ("a_stride", C.c_int64 * 3), ("b_stride", C.c_int64 * 3),
         ("c_stride", C.c_int64 * 3), ("dt_stride", C.c_int64 * 3), ("y_stride", C.c_int64 * 3),
+        ("D", C.c_void_p), ("Z", C.c_void_p), ("z_stride", C.c_int64 * 3),
     ]
 
 

@@ -9,7 +9,7 @@
 
 namespace {
 
-constexpr int kAbiVersion = 1;
+constexpr int kAbiVersion = 2;
 constexpr int kSmCount = 148;  // B200
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -84,12 +84,14 @@ bool strides_mult(const int64_t* s, int m) { return s[0] % m == 0 && s[1] % m ==
 void fill_params(const SsdArgs* a, ssd::ScanParams* p) {
   std::memset(p, 0, sizeof(*p));
   p->X = a->X; p->A = a->A; p->B = a->B; p->C = a->C; p->dt = a->dt; p->Y = a->Y;
+  p->D = a->D; p->Z = a->Z;
   p->status = a->status;
   p->batch = a->batch; p->seqlen = a->seqlen; p->nheads = a->nheads; p->p = a->headdim; p->n = a->dstate;
   p->ngroups = a->ngroups;
   for (int i = 0; i < 3; ++i) {
     p->xs[i] = a->x_stride[i]; p->as[i] = a->a_stride[i]; p->bs[i] = a->b_stride[i];
     p->cs[i] = a->c_stride[i]; p->dts[i] = a->dt_stride[i]; p->ys[i] = a->y_stride[i];
+    p->zs[i] = a->z_stride[i];
   }
   const int per16 = 16 / elem_size(a->dtype);
   bool v = aligned16(a->X) && aligned16(a->B) && strides_mult(a->x_stride, per16) &&
@@ -162,7 +164,9 @@ size_t ssd_b200_workspace_bytes(const SsdArgs* args) {
   return 2 * align_up(units * nseg * np * sizeof(float), 256) + 2 * align_up(units * nseg * sizeof(float), 256);
 }
 
-int ssd_b200_forward(const SsdArgs* args, void* stream_v) {
+// The forward proper.  `fuse_epilogue`: the selected kernel applies D / Z itself; otherwise they are dropped here
+// and ssd_b200_forward() runs the stand-alone epilogue kernel afterwards.
+static int forward_impl(const SsdArgs* args, void* stream_v, bool fuse_epilogue) {
   int rc = validate(args);
   if (rc != SSD_OK) return rc;
   rc = validate_pointers(args);
@@ -183,6 +187,7 @@ int ssd_b200_forward(const SsdArgs* args, void* stream_v) {
   fill_params(args, &prm);
   prm.seg_len = seg_len;
   prm.nseg = nseg;
+  if (!fuse_epilogue || state_only) prm.D = nullptr, prm.Z = nullptr;
 
   if (nseg <= 1) {
     prm.compute_y = state_only ? 0 : 1;
@@ -258,6 +263,21 @@ int ssd_b200_forward(const SsdArgs* args, void* stream_v) {
   p2.fin = nullptr;
   p2.fin_ld = nullptr;
   return launch_kernel(kernel, args, p2, stream);
+}
+
+int ssd_b200_forward(const SsdArgs* args, void* stream_v) {
+  int rc = validate(args);
+  if (rc != SSD_OK) return rc;
+  const bool state_only = (args->flags & SSD_FLAG_STATE_ONLY) != 0;
+  if (state_only || (!args->D && !args->Z)) return forward_impl(args, stream_v, false);
+  // skip and gate of model_ref.py:116-118: fused into the two-head tensor-core kernel, a kernel of their own otherwise
+  const int kernel = resolve_kernel(args);
+  const bool fuse = kernel == SSD_KERNEL_TCGEN05 && ssd::tc_supports(*args) && use_tc2(args);
+  rc = forward_impl(args, stream_v, fuse);
+  if (rc != SSD_OK || fuse) return rc;
+  ssd::ScanParams ep;
+  fill_params(args, &ep);
+  return ssd::launch_epilogue(ep, args->dtype, static_cast<cudaStream_t>(stream_v));
 }
 
 int ssd_b200_fold_states(const float* states, int64_t states_shard_stride, const float* logdecay,

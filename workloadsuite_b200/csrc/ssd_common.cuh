@@ -41,13 +41,16 @@ struct ScanParams {
   int seg_len, nseg;
   int compute_y;
   int vec_ok;          // all row starts 16-byte aligned
-  // Chained segments (two-head tensor-core kernel only): segment k of a unit starts from the state that
-  // segment k-1 of the same unit left in chain_state, once chain_flag says it is there.
+  // Chained mode (two-head tensor-core kernel only): a piece of a sequence starts from the state that the
+  // piece before it (on the neighbouring CTA) left in chain_state, once chain_flag says it is there.
   int chain;
-  float* chain_state;     // [unit][nseg][n*p]
-  float* chain_ld;        // [unit][nseg] running sum of the log-decay up to the end of the segment
-  int32_t* chain_flag;    // [unit][nseg], zeroed before the launch
-  int64_t xs[3], as[3], bs[3], cs[3], dts[3], ys[3];
+  float* chain_state;     // [slot][n*p], slot = 2 * CTA + head of the pair
+  float* chain_ld;        // [slot] running sum of the log-decay up to the end of the piece
+  int32_t* chain_flag;    // [slot], zeroed before the launch
+  // Optional epilogue Y <- (Y + x * D[head]) * silu(z) (model_ref.py:116-118); either pointer may be null.
+  const float* D;         // [h]
+  const void* Z;          // [b,s,h,p], strides zs
+  int64_t xs[3], as[3], bs[3], cs[3], dts[3], ys[3], zs[3];
 };
 
 template <typename T> struct Cvt;
@@ -69,6 +72,9 @@ template <> struct Cvt<__nv_bfloat16> {
 int launch_scan_f32(const ScanParams& prm, int dtype, cudaStream_t stream);
 bool scan_f32_supports(int p, int n);
 int scan_f32_tile_tokens();
+
+// Y <- (Y + x * D[head]) * silu(z) in place over [b,s,h,p] (for the kernels that do not fuse it).
+int launch_epilogue(const ScanParams& p, int dtype, cudaStream_t stream);
 
 // `incoming` (nullable, may alias `states`) receives the state entering every segment, in the layout of `states`.
 int launch_fold(const float* states, int64_t st_unit_stride, int64_t st_seg_stride, const float* ld,

@@ -94,6 +94,7 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
   if (!host->X || !host->A || !host->B) return SSD_ERR_NULL_POINTER;
   if (!state_only && (!host->Y || !host->C)) return SSD_ERR_NULL_POINTER;
   if (state_only && !host->final_state) return SSD_ERR_NULL_POINTER;
+  if (host->D || host->Z) return SSD_ERR_UNSUPPORTED;   // the skip/gate epilogue is a device-buffer feature
   const Plan pl = make_plan(host);
   if (!dev_scratch || dev_scratch_bytes < pl.total_bytes) return SSD_ERR_WORKSPACE;
   if (reinterpret_cast<uintptr_t>(dev_scratch) & 255) return SSD_ERR_MISALIGNED;

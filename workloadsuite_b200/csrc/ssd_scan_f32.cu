@@ -8,6 +8,7 @@
 // n_i = (k*SL + sl)*4 + q, so the B/C rows are read from shared memory as
 // conflict-free float4 broadcasts and y_t is finished by a shuffle over the SL
 // lanes that share a column.
+#include <algorithm>
 #include "ssd_common.cuh"
 
 namespace ssd {
@@ -314,6 +315,49 @@ int launch_scan_f32(const ScanParams& prm, int dtype, cudaStream_t stream) {
     case SSD_DTYPE_BF16: return launch_t<__nv_bfloat16>(prm, stream);
     default: return SSD_ERR_UNSUPPORTED;
   }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Skip and gate of SSDLayer.forward after the core (model_ref.py:116-118), for the kernels that do
+// not fuse it:  Y <- (Y + x * D[head]) * silu(z), fp32 arithmetic, one rounding.  One thread per
+// 8 consecutive head-dim elements (16 bytes of a 16-bit row; rows are 16-byte aligned when vec_ok).
+template <typename T>
+__global__ void __launch_bounds__(256)
+ssd_epilogue_kernel(const ScanParams p) {
+  const int vec = p.p / 8;
+  const int64_t total = (int64_t)p.batch * p.seqlen * p.nheads * vec;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int v = (int)(i % vec);
+    int64_t r = i / vec;
+    const int hh = (int)(r % p.nheads); r /= p.nheads;
+    const int t = (int)(r % p.seqlen);
+    const int b = (int)(r / p.seqlen);
+    T* y = static_cast<T*>(p.Y) + b * p.ys[0] + (int64_t)t * p.ys[1] + hh * p.ys[2] + 8 * v;
+    const T* x = static_cast<const T*>(p.X) + b * p.xs[0] + (int64_t)t * p.xs[1] + hh * p.xs[2] + 8 * v;
+    const T* z = p.Z ? static_cast<const T*>(p.Z) + b * p.zs[0] + (int64_t)t * p.zs[1] + hh * p.zs[2] + 8 * v : nullptr;
+    const float d = p.D ? p.D[hh] : 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float acc = Cvt<T>::to_f(y[e]);
+      if (p.D) acc = fmaf(Cvt<T>::to_f(x[e]), d, acc);
+      if (z) {
+        const float zz = Cvt<T>::to_f(z[e]);
+        acc *= zz / (1.f + __expf(-zz));
+      }
+      y[e] = Cvt<T>::from_f(acc);
+    }
+  }
+}
+
+int launch_epilogue(const ScanParams& p, int dtype, cudaStream_t stream) {
+  if (!p.D && !p.Z) return SSD_OK;
+  if (p.p % 8 != 0) return SSD_ERR_UNSUPPORTED;
+  const int64_t total = (int64_t)p.batch * p.seqlen * p.nheads * (p.p / 8);
+  const int grid = (int)std::min<int64_t>((total + 255) / 256, 148 * 16);
+  if (dtype == SSD_DTYPE_F32) ssd_epilogue_kernel<float><<<grid, 256, 0, stream>>>(p);
+  else if (dtype == SSD_DTYPE_F16) ssd_epilogue_kernel<__half><<<grid, 256, 0, stream>>>(p);
+  else ssd_epilogue_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? SSD_OK : SSD_ERR_CUDA;
 }
 
 int launch_fold(const float* states, int64_t st_unit_stride, int64_t st_seg_stride, const float* ld,

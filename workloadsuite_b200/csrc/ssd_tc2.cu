@@ -175,7 +175,8 @@ constexpr int kTr0 = SSD_TC2_TRACE_FIRST, kTrN = 6, kTrEv = 24;
 #define ITRACE(idx) {}
 #endif
 
-template <typename T16, int N>
+// EPI: apply the skip and gate of model_ref.py:116-118 to Y on its way out (sp.D / sp.Z; either may be null).
+template <typename T16, int N, bool EPI>
 __global__ void __launch_bounds__(kThreads2, 1)
 ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmY,
@@ -426,6 +427,10 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 #define CTRACE(ev) { if (h == 0 && l == 96) TRACE(ev, it) }
     float H[P];
     float cs = 0.f, tot = 0.f, cs2 = 0.f;   // of the tile whose P / Y is being produced
+    // dt multiplies the columns of P instead of the rows of X (P.(dt o x) = (P o dt_s).x), so the X tile stays as
+    // loaded: this row's value as a column of the diagonal mask block is cs2 - log2(dt) (clamped: dt == 0 must not
+    // break the chain of per-token factors there; the clamped column then weighs 2^-60, i.e. nothing).
+    float cs2c = 0.f;
     float a_next = 0.f, dt_next = 1.f;   // log-decay / dt of this thread's row in the next tile to be scanned
     bool next_prefetched = false;
     bool store_pending = false;    // (thread l == 0) a TMA store of Y is in flight from X stage store_stage
@@ -433,7 +438,8 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     float asum = 0.f, acomp = 0.f;   // compensated (Kahan) sum of the tile totals; FP64 is slow on this part
 
     // prefix sum of the log-decay over the 128 rows (model_ref.py:135); publishes cs*log2(e) for the P step
-    auto scan_tile = [&](float a, uint32_t par, bool sync_after, float& cs_o, float& tot_o, float& cs2_o) {
+    auto scan_tile = [&](float a, float dtv, uint32_t par, bool sync_after, float& cs_o, float& tot_o, float& cs2_o,
+                         float& cs2c_o) {
       float v = a;
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {
@@ -449,35 +455,31 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       tot_o = (w0 + w1 + w2) + w3;
       cs2_o = cs_o * kLog2e;
       // column factor of the factored decay mask: exp(cs at the end of this row's 32-token block - cs_row)
-      m->cf[h][par][l] = ex2(__shfl_sync(0xffffffffu, cs2_o, 31) - cs2_o);
+      // (times dt of the row: the factor belongs to the row as a column of P)
+      m->cf[h][par][l] = ex2(__shfl_sync(0xffffffffu, cs2_o, 31) - cs2_o) * dtv;
+      cs2c_o = cs2_o - fmaxf(__log2f(dtv), -60.f);
       if (lane == 31) m->cend[h][par][q] = cs2_o;
       // cf / cend are read one tile later and the warp sums are rewritten one tile later: the barrier of the Y
       // read-out lies in between, except after an item's first tile and in state-only mode
       if (sync_after) named_bar_sync(bar_id, 128);
       PROF(13)
     };
-    // Xd = exp(cs_last - cs_l) * x~ (model_ref.py:144,148) from X stage `st` into this head's Xd buffer
-    auto make_xd = [&](uint32_t st, float cs_t, float tot_t, float dtv, bool has_dt) {
-      const float dl = ex2((tot_t - cs_t) * kLog2e);
+    // Xd = exp(cs_last - cs_l) * dt * x (model_ref.py:144,148) from X stage `st` into this head's Xd buffer
+    auto make_xd = [&](uint32_t st, float cs_t, float tot_t, float dtv) {
+      const float dl = ex2((tot_t - cs_t) * kLog2e) * dtv;
       const uint32_t xrow = sX + (kXStages * h + st) * kBlk + l * 128, xdrow = sXdh + l * 128;
       // packed 16-bit arithmetic, as the reference does for X*dt and the decay-scaled X (model_ref.py:144,148)
-      const uint32_t dl2 = pack2<T16>(dl, dl), dt2 = pack2<T16>(dtv, dtv);
+      const uint32_t dl2 = pack2<T16>(dl, dl);
       uint4 rawv[8];
 #pragma unroll
       for (int c = 0; c < 8; ++c) rawv[c] = lds128(xrow + ((c ^ swz) << 4));   // all loads first: their latencies overlap
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
-        const uint32_t phys = (c ^ swz) << 4;
-        uint4 raw = rawv[c];
-        if (has_dt) {
-          raw.x = mul2<T16>(raw.x, dt2); raw.y = mul2<T16>(raw.y, dt2);
-          raw.z = mul2<T16>(raw.z, dt2); raw.w = mul2<T16>(raw.w, dt2);
-          sts128(xrow + phys, raw);   // x~ replaces x as the operand of P . X
-        }
+        const uint4 raw = rawv[c];
         uint4 o;
         o.x = mul2<T16>(raw.x, dl2); o.y = mul2<T16>(raw.y, dl2);
         o.z = mul2<T16>(raw.z, dl2); o.w = mul2<T16>(raw.w, dl2);
-        sts128(xdrow + phys, o);
+        sts128(xdrow + ((c ^ swz) << 4), o);
       }
     };
     auto store_hb = [&]() {
@@ -499,6 +501,16 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     int y_hi = 0, y_t0 = 0, y_bi = 0;
     auto finish_y = [&]() -> bool {
       PROF(20)
+      // (EPI) this row of the gate: 128 contiguous bytes, fetched ahead of the wait for the MMA
+      uint4 zr[8];
+      if constexpr (EPI) {
+        if (sp.Z) {
+          const uint4* zrow = reinterpret_cast<const uint4*>(static_cast<const T16*>(sp.Z) + y_bi * sp.zs[0] +
+                                                              (int64_t)(y_t0 + l) * sp.zs[1] + y_hi * sp.zs[2]);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) zr[c] = __ldg(zrow + c);
+        }
+      }
       if (!cwait(&m->bar_y[h], y_it & 1, STATUS_WAIT_TIMEOUT_MMA)) return false;
       if (h == 0 && l == 96) TRACE(8, y_it)
       PROF(17)
@@ -513,6 +525,38 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         tmem_ld32(tY + tlane + 32, y1);
         tmem_ld_wait();
       PROF(18)
+        tc_fence_before();
+        if (h == 0 && l == 96) TRACE(9, y_it)
+        warp_arrive(&m->bar_e);   // the Y accumulator is read out: the next tile's C.H may overwrite it
+        if constexpr (EPI) {
+          // Y <- (Y + x * D) * silu(z) (model_ref.py:116-118) in fp32; x is this thread's row of the X tile, still in
+          // the stage that the Y rows go to; silu(z) = z * (0.5 + 0.5 tanh(z / 2)), the tanh on 16-bit pairs.
+          const float dskip = sp.D ? sp.D[y_hi] : 0.f;
+          const bool gate = sp.Z != nullptr;
+          const uint32_t half2 = pack2<T16>(0.5f, 0.5f);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const uint4 xr = lds128(ystage + l * 128 + ((c ^ swz) << 4));
+            const uint32_t xw[4] = {xr.x, xr.y, xr.z, xr.w};
+            const uint32_t zw[4] = {zr[c].x, zr[c].y, zr[c].z, zr[c].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              uint32_t* yy = (c < 4) ? &y0[8 * c + 2 * e] : &y1[8 * (c - 4) + 2 * e];
+              float v0 = __uint_as_float(yy[0]), v1 = __uint_as_float(yy[1]);
+              const float2 xf = unpack2<T16>(xw[e]);
+              v0 = fmaf(xf.x, dskip, v0);
+              v1 = fmaf(xf.y, dskip, v1);
+              if (gate) {
+                const float2 zf = unpack2<T16>(zw[e]);
+                const float2 th = unpack2<T16>(tanh2<T16>(mul2<T16>(zw[e], half2)));
+                v0 *= zf.x * fmaf(0.5f, th.x, 0.5f);
+                v1 *= zf.y * fmaf(0.5f, th.y, 0.5f);
+              }
+              yy[0] = __float_as_uint(v0);
+              yy[1] = __float_as_uint(v1);
+            }
+          }
+        }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint4 o;
@@ -533,9 +577,6 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         }
       }
       PROF(19)
-      tc_fence_before();
-      if (h == 0 && l == 96) TRACE(9, y_it)
-      warp_arrive(&m->bar_e);   // the Y accumulator is read out: the next tile's C.H may overwrite it
       fence_proxy_async();         // staged rows -> visible to the TMA engine
       named_bar_sync(bar_id, 128);
       if (l == 0) {
@@ -556,9 +597,12 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     };
 
     const Work wk = m->work;
-    for (int wi = 0; wi < wk.count && ok; ++wi) {
-      const Item w = work_item(prm, wk, wi);
-      if (w.ntiles == 0) continue;
+    // (one pass more than there are items: an empty item whose only iteration reads out the last Y tile, so that
+    //  the read-out code exists once)
+    for (int wi = 0; wi <= wk.count && ok; ++wi) {
+      Item w = {};
+      if (wi < wk.count) w = work_item(prm, wk, wi);
+      if (w.ntiles == 0 && wi < wk.count) continue;
       if (h == 0 && l == 96) ITRACE(1 + wi)
       const int hi = w.h0 + h;
       const int64_t unit = (int64_t)w.bi * sp.nheads + hi;
@@ -568,7 +612,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       float asum0 = 0.f;   // log-decay summed over the earlier segments of a chained sequence
       asum = 0.f;
       acomp = 0.f;
-      if (!next_prefetched) {   // (the first item of this CTA; later items were prefetched during their predecessor)
+      if (!next_prefetched && w.ntiles > 0) {   // (the first item of this CTA; later items were prefetched during their predecessor)
         a_next = Ag[(int64_t)(w.t_begin + l) * sp.as[1]];
         dt_next = Dg ? Cvt<T16>::to_f(Dg[(int64_t)(w.t_begin + l) * sp.dts[1]]) : 1.f;
       }
@@ -658,7 +702,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           if (!ok) break;
         }
         // ---- c. next tile: prefix sum and Xd (the S MMA that read the Xd buffer was waited for in step a)
-        float cs_n = 0.f, tot_n = 0.f, cs2_n = 0.f;
+        float cs_n = 0.f, tot_n = 0.f, cs2_n = 0.f, cs2c_n = 0.f;
         if (have_next) {
           const uint32_t itn = (j >= 0) ? it + 1 : it;
           const float a = a_next, dtv = dt_next;
@@ -666,13 +710,13 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             a_next = Ag[(int64_t)(t0 + 2 * T + l) * sp.as[1]];
             if (Dg) dt_next = Cvt<T16>::to_f(Dg[(int64_t)(t0 + 2 * T + l) * sp.dts[1]]);
           }
-          scan_tile(a, itn & 1, j < 0 || !want_y, cs_n, tot_n, cs2_n);
+          scan_tile(a, dtv, itn & 1, j < 0 || !want_y, cs_n, tot_n, cs2_n, cs2c_n);
           if (h == 0 && l == 96) TRACE(18, itn)
           ok = cwait(&m->full_x[h][itn % kXStages], (itn / kXStages) & 1, STATUS_WAIT_TIMEOUT_TMA);
           if (!ok) break;
           if (h == 0 && l == 96) TRACE(19, itn)
         PROF(14)
-          make_xd(itn % kXStages, cs_n, tot_n, dtv, Dg != nullptr);
+          make_xd(itn % kXStages, cs_n, tot_n, dtv);
         PROF(15)
           fence_proxy_async();
           warp_arrive(&m->bar_xd);
@@ -682,7 +726,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         PROF(16)
         // ---- state entering the item (after the first tile's Xd is on its way to the S MMA: the wait for a
         //      chained predecessor and the state load then overlap that MMA)
-        if (j == -1) {
+        if (j == -1 && w.ntiles > 0) {
           if (w.in_slot >= 0) {
             // wait (bounded) for the previous segment of this unit, which another CTA may still be finishing
             const int64_t slot = 2 * w.in_slot + h;
@@ -755,11 +799,11 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
               // One ex2 per four columns: exp(cs_l - cs_{s+1}) = exp(cs_l - cs_s) * exp(-a_{s+1}), the per-token
               // factor exp(-a) coming from the lane that owns the row (clamped: an entry above the diagonal may
               // overflow, it is masked out by a select, never multiplied into anything that is kept).
-              const float einv = ex2(fminf(__shfl_up_sync(0xffffffffu, cs2, 1) - cs2, 126.f));
+              const float einv = ex2(fminf(__shfl_up_sync(0xffffffffu, cs2c, 1) - cs2c, 126.f));
               uint32_t pk[16];
 #pragma unroll
               for (int e4 = 0; e4 < 8; ++e4) {
-                const float c0 = __shfl_sync(0xffffffffu, cs2, 4 * e4);   // cs of the column: from the lane owning that row
+                const float c0 = __shfl_sync(0xffffffffu, cs2c, 4 * e4);   // the column's value: from the lane owning that row
                 const float f1 = __shfl_sync(0xffffffffu, einv, 4 * e4 + 1), f2 = __shfl_sync(0xffffffffu, einv, 4 * e4 + 2);
                 const float f3 = __shfl_sync(0xffffffffu, einv, 4 * e4 + 3);
                 const float w0 = ex2(cs2 - c0), w1 = w0 * f1, w2 = w1 * f2, w3 = w2 * f3;
@@ -843,14 +887,13 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           }
           ++it;
         }
-        cs = cs_n; tot = tot_n; cs2 = cs2_n;
+        cs = cs_n; tot = tot_n; cs2 = cs2_n; cs2c = cs2c_n;
       }
       if (!ok) break;
 
     }
-    if (ok && y_pending) ok = finish_y();
     if (h == 0 && l == 96) ITRACE(30)
-    if (l == 0 && store_pending) bulk_wait_all();   // the last Y tile must have left shared memory
+    if (l == 0) bulk_wait_all();   // the Y tiles this thread stored must have landed before the CTA exits
 #ifdef SSD_TC2_PROFILE
     if (blockIdx.x == 0 && h == 0 && (l == 0 || l == 96) && status) {
       for (int i = 0; i < 24; ++i) status[2 + 24 * (l / 96) + i] = (int)(prof[i] >> 4);   // cycles / 16
@@ -871,10 +914,10 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   }
 }
 
-template <typename T16, int N>
+template <typename T16, int N, bool EPI>
 int launch_typed2(const CUtensorMap& tx, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& ty,
                   const Tc2Params& prm, cudaStream_t stream) {
-  auto kern = ssd_tc2_kernel<T16, N>;
+  auto kern = ssd_tc2_kernel<T16, N, EPI>;
   constexpr int smem = Layout2<N>::kBytes;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
     return SSD_ERR_CUDA;
@@ -947,11 +990,22 @@ int launch_tc2(const SsdArgs& a, const ScanParams& sp, cudaStream_t stream) {
     tc = tb;
     ty = tx;
   }
+  const bool epi = sp.compute_y && (sp.D || sp.Z);
+  if (epi) {
+    // the gate rows are read with 16-byte loads
+    if (sp.Z && ((reinterpret_cast<uintptr_t>(sp.Z) & 15) || sp.zs[0] % 8 || sp.zs[1] % 8 || sp.zs[2] % 8))
+      return SSD_ERR_MISALIGNED;
+    if (a.dtype == SSD_DTYPE_BF16)
+      return a.dstate == 128 ? launch_typed2<__nv_bfloat16, 128, true>(tx, tb, tc, ty, prm, stream)
+                             : launch_typed2<__nv_bfloat16, 64, true>(tx, tb, tc, ty, prm, stream);
+    return a.dstate == 128 ? launch_typed2<__half, 128, true>(tx, tb, tc, ty, prm, stream)
+                           : launch_typed2<__half, 64, true>(tx, tb, tc, ty, prm, stream);
+  }
   if (a.dtype == SSD_DTYPE_BF16)
-    return a.dstate == 128 ? launch_typed2<__nv_bfloat16, 128>(tx, tb, tc, ty, prm, stream)
-                           : launch_typed2<__nv_bfloat16, 64>(tx, tb, tc, ty, prm, stream);
-  return a.dstate == 128 ? launch_typed2<__half, 128>(tx, tb, tc, ty, prm, stream)
-                         : launch_typed2<__half, 64>(tx, tb, tc, ty, prm, stream);
+    return a.dstate == 128 ? launch_typed2<__nv_bfloat16, 128, false>(tx, tb, tc, ty, prm, stream)
+                           : launch_typed2<__nv_bfloat16, 64, false>(tx, tb, tc, ty, prm, stream);
+  return a.dstate == 128 ? launch_typed2<__half, 128, false>(tx, tb, tc, ty, prm, stream)
+                         : launch_typed2<__half, 64, false>(tx, tb, tc, ty, prm, stream);
 }
 
 }  // namespace ssd

@@ -44,6 +44,21 @@ __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// tanh of a packed pair of 16-bit values (one MUFU operation for the pair)
+template <typename T16>
+__device__ __forceinline__ uint32_t tanh2(uint32_t v);
+template <>
+__device__ __forceinline__ uint32_t tanh2<__nv_bfloat16>(uint32_t v) {
+  uint32_t r;
+  asm("tanh.approx.bf16x2 %0, %1;" : "=r"(r) : "r"(v));
+  return r;
+}
+template <>
+__device__ __forceinline__ uint32_t tanh2<__half>(uint32_t v) {
+  uint32_t r;
+  asm("tanh.approx.f16x2 %0, %1;" : "=r"(r) : "r"(v));
+  return r;
+}
 // Packed 16-bit multiply of two values by one scalar (both given as packed pairs).  The reference forms
 // X*dt and the decay-scaled operands in half precision too (model_ref.py:144,148).
 template <typename T16>

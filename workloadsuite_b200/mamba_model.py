@@ -28,8 +28,9 @@ from workloadsuite_b200.ssd import ssd_forward  # noqa: E402
 
 
 @torch.compiler.disable
-def _core(x, A_dt, B, C, dt, block_len):
-    return ssd_forward(x, A_dt, B, C, block_len, dt=dt)
+def _core(x, A_dt, B, C, dt, block_len, D, z):
+    """The SSD core with the layer's skip and gate (``model_ref.py:116-118``) applied in the kernel's epilogue."""
+    return ssd_forward(x, A_dt, B, C, block_len, dt=dt, D=D, z=z)
 
 
 def _tma_friendly(t: torch.Tensor) -> torch.Tensor:
@@ -83,12 +84,9 @@ class SSDLayer(nn.Module):
         dt = F.softplus(dt + self.dt_bias)
         A_dt = -torch.exp(self.A_log) * dt.float()
 
-        Y = _core(x, A_dt, B, C, dt, self.block_len)
-
-        Y = Y + x * self.D.view(1, 1, -1, 1)
-        Y = Y.view(batch, seq_len, self.d_inner)
-        Y = Y * F.silu(z)
-        return self.out_proj(Y)
+        z = _tma_friendly(z.unflatten(-1, (self.n_heads, self.d_head)))     # a view of the projection output
+        Y = _core(x, A_dt, B, C, dt, self.block_len, self.D, z)             # (Y + x D) silu(z), model_ref.py:116-118
+        return self.out_proj(Y.view(batch, seq_len, self.d_inner))
 
 
 class Model(nn.Module):

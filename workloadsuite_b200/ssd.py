@@ -144,6 +144,8 @@ def ssd_forward(
     nsegments: Optional[int] = None,
     out: Optional[torch.Tensor] = None,
     reuse_segments: bool = False,
+    D: Optional[torch.Tensor] = None,
+    z: Optional[torch.Tensor] = None,
 ):
     """Mamba-2 SSD forward ``Y = SSD(X, A, B, C)`` on the current CUDA stream.
 
@@ -155,6 +157,10 @@ def ssd_forward(
     reference's ``block_len``: it must divide ``s`` (as at ``model_ref.py:106``);
     the result does not otherwise depend on it.  Views with a contiguous innermost
     axis are accepted as they are.  No host synchronisation.
+
+    ``D`` [h] and ``z`` [b,s,h,p] (dtype of X) add the layer's skip and gate to the kernel's epilogue:
+    ``Y <- (Y + X * D[head]) * silu(z)`` (``model_ref.py:116-118``), evaluated in float32 and rounded once;
+    either may be given alone.  Note that the skip term uses ``X`` as passed, i.e. before ``dt``.
 
     Returns Y [b,s,h,p] in X's dtype, plus the float32 final state [b,h,n,p] and/or
     the summed log-decay [b,h] when asked.  With ``state_only`` no Y is produced.
@@ -168,6 +174,14 @@ def ssd_forward(
         raise ValueError("n_heads must be divisible by n_groups")
     if initial_states is not None:
         initial_states = initial_states.contiguous()
+    if D is not None:
+        if D.shape != (h,):
+            raise ValueError("D must be [h]")
+        D = D.to(device=X.device, dtype=torch.float32).contiguous()
+    if z is not None and (z.shape != X.shape or z.dtype != X.dtype or not z.is_cuda):
+        raise ValueError("z must be a CUDA tensor [b,s,h,p] in the dtype of X")
+    if state_only and (D is not None or z is not None):
+        raise ValueError("D / z apply to Y; a state-only run produces none")
     lib = _lib.load()
     dev = X.device
     want_final = return_final_state or state_only
@@ -179,6 +193,11 @@ def ssd_forward(
     args = _lib.SsdArgs()
     _fill(args, X, A, B, C_, dt, initial_states, Y, final_state, final_ld, chunk, kernel, nsegments, state_only,
           reuse_segments)
+    if D is not None:
+        args.D = D.data_ptr()
+    if z is not None:
+        args.Z = z.data_ptr()
+        args.z_stride = _strides3(z, "z")
     with torch.cuda.device(dev):
         need = lib.ssd_b200_workspace_bytes(C.byref(args))
         ws = _workspace(dev, need)
