@@ -429,6 +429,40 @@ def main():
             except Exception as exc:
                 others[name] = {"error": f"{type(exc).__name__}: {exc}"}
 
+        # The same workload with the layer's skip and gate, (Y + x D) silu(z) of model_ref.py:116-118, fused into the
+        # kernel's epilogue, next to the same three steps done as separate PyTorch passes over Y.
+        try:
+            c = CONFIGS[args.workload]
+            sb = algorithmic_bytes(c) + c["b"] * c["s"] * c["h"] * c["p"] * 2   # + one read of z
+            ns = min(16, max(2, int(math.ceil(2.5 * L2_BYTES / sb))))
+            ss = [gen_inputs(c, dev, seed=177 + i) for i in range(ns)]
+            oo = [torch.empty_like(x["X"]) for x in ss]
+            zz = [torch.randn_like(x["X"]) for x in ss]
+            Dv = torch.randn(c["h"], device=dev)
+
+            def st_fused(i):
+                d = ss[i]
+                W.ssd_forward(d["X"], d["A"], d["B"], d["C"], c["chunk"], initial_states=d.get("initial_states"),
+                              out=oo[i], kernel=args.kernel, D=Dv, z=zz[i])
+
+            def st_unfused(i):
+                d = ss[i]
+                Y = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], c["chunk"], initial_states=d.get("initial_states"),
+                                  out=oo[i], kernel=args.kernel)
+                Y = Y + d["X"] * Dv.to(Y.dtype).view(1, 1, -1, 1)
+                Y = Y * torch.nn.functional.silu(zz[i])
+
+            ms_f, _, _ = time_steps(st_fused, ns, max(5, args.steps // 2), 3, False)
+            ms_u, _, _ = time_steps(st_unfused, ns, max(5, args.steps // 2), 3, False)
+            others[args.workload + "+skip_gate"] = {
+                "tokens_per_s": c["b"] * c["s"] / (ms_f * 1e-3), "ms_per_step": ms_f,
+                "hbm_frac_of_measured": sb / (ms_f * 1e-3) / 1e9 / peak,
+                "ms_per_step_with_pytorch_epilogue": ms_u}
+            del ss, oo, zz
+            torch.cuda.empty_cache()
+        except Exception as exc:
+            others[args.workload + "+skip_gate"] = {"error": f"{type(exc).__name__}: {exc}"}
+
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:

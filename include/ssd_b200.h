@@ -52,10 +52,12 @@ enum {
 /* flags */
 enum {
   SSD_FLAG_STATE_ONLY = 1,/* do not compute/write Y; only final_state / final_logdecay */
-  SSD_FLAG_REUSE_SEGMENTS = 2 /* two-pass segmented scan only: the workspace still holds the per-segment
+  SSD_FLAG_REUSE_SEGMENTS = 2,/* two-pass segmented scan only: the workspace still holds the per-segment
                                  results of the previous call on this stream with SSD_FLAG_STATE_ONLY, the same
                                  tensors, sizes and nsegments; do not recompute them (a sequence-sharded
                                  forward runs state-only first, exchanges states, then runs with this flag) */
+  SSD_FLAG_SEPARATE_EPILOGUE = 4 /* apply D / Z with the stand-alone epilogue kernel even where the main kernel
+                                    could fuse them (for comparisons) */
 };
 
 /*

@@ -22,6 +22,7 @@ DTYPE_F32, DTYPE_F16, DTYPE_BF16 = 0, 1, 2
 KERNEL_AUTO, KERNEL_SCAN_F32, KERNEL_TCGEN05 = 0, 1, 2
 FLAG_STATE_ONLY = 1
 FLAG_REUSE_SEGMENTS = 2
+FLAG_SEPARATE_EPILOGUE = 4
 
 # every symbol include/ssd_b200.h declares
 EXPORTS = (

@@ -98,6 +98,7 @@ void fill_params(const SsdArgs* a, ssd::ScanParams* p) {
            strides_mult(a->b_stride, per16) && a->headdim % 8 == 0 && a->dstate % 8 == 0;
   if (a->C) v = v && aligned16(a->C) && strides_mult(a->c_stride, per16);
   if (a->Y) v = v && aligned16(a->Y) && strides_mult(a->y_stride, per16);
+  if (a->Z) v = v && aligned16(a->Z) && strides_mult(a->z_stride, per16);
   p->vec_ok = v ? 1 : 0;
 }
 
@@ -272,7 +273,8 @@ int ssd_b200_forward(const SsdArgs* args, void* stream_v) {
   if (state_only || (!args->D && !args->Z)) return forward_impl(args, stream_v, false);
   // skip and gate of model_ref.py:116-118: fused into the two-head tensor-core kernel, a kernel of their own otherwise
   const int kernel = resolve_kernel(args);
-  const bool fuse = kernel == SSD_KERNEL_TCGEN05 && ssd::tc_supports(*args) && use_tc2(args);
+  const bool fuse = kernel == SSD_KERNEL_TCGEN05 && ssd::tc_supports(*args) && use_tc2(args) &&
+                    !(args->flags & SSD_FLAG_SEPARATE_EPILOGUE);
   rc = forward_impl(args, stream_v, fuse);
   if (rc != SSD_OK || fuse) return rc;
   ssd::ScanParams ep;

@@ -336,15 +336,40 @@ ssd_epilogue_kernel(const ScanParams p) {
     const T* x = static_cast<const T*>(p.X) + b * p.xs[0] + (int64_t)t * p.xs[1] + hh * p.xs[2] + 8 * v;
     const T* z = p.Z ? static_cast<const T*>(p.Z) + b * p.zs[0] + (int64_t)t * p.zs[1] + hh * p.zs[2] + 8 * v : nullptr;
     const float d = p.D ? p.D[hh] : 0.f;
+    // eight elements per thread, moved as whole 16-byte (32-byte for fp32) vectors when the rows allow it
+    T yv[8], xv[8], zv[8];
+    constexpr int kVecs = sizeof(T) * 8 / 16;
+    if (p.vec_ok) {
+#pragma unroll
+      for (int k = 0; k < kVecs; ++k) {
+        reinterpret_cast<uint4*>(yv)[k] = reinterpret_cast<const uint4*>(y)[k];
+        if (p.D) reinterpret_cast<uint4*>(xv)[k] = reinterpret_cast<const uint4*>(x)[k];
+        if (z) reinterpret_cast<uint4*>(zv)[k] = reinterpret_cast<const uint4*>(z)[k];
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        yv[e] = y[e];
+        if (p.D) xv[e] = x[e];
+        if (z) zv[e] = z[e];
+      }
+    }
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      float acc = Cvt<T>::to_f(y[e]);
-      if (p.D) acc = fmaf(Cvt<T>::to_f(x[e]), d, acc);
+      float acc = Cvt<T>::to_f(yv[e]);
+      if (p.D) acc = fmaf(Cvt<T>::to_f(xv[e]), d, acc);
       if (z) {
-        const float zz = Cvt<T>::to_f(z[e]);
+        const float zz = Cvt<T>::to_f(zv[e]);
         acc *= zz / (1.f + __expf(-zz));
       }
-      y[e] = Cvt<T>::from_f(acc);
+      yv[e] = Cvt<T>::from_f(acc);
+    }
+    if (p.vec_ok) {
+#pragma unroll
+      for (int k = 0; k < kVecs; ++k) reinterpret_cast<uint4*>(y)[k] = reinterpret_cast<const uint4*>(yv)[k];
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y[e] = yv[e];
     }
   }
 }

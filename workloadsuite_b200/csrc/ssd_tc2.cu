@@ -501,14 +501,18 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     int y_hi = 0, y_t0 = 0, y_bi = 0;
     auto finish_y = [&]() -> bool {
       PROF(20)
-      // (EPI) this row of the gate: 128 contiguous bytes, fetched ahead of the wait for the MMA
+      // (EPI) the gate rows of this warp's 32 tokens, fetched ahead of the wait for the MMA.  Eight lanes read one
+      // 128-byte row per load (whole lines), four rows per instruction; the rows reach their threads through the
+      // staging buffer below.
       uint4 zr[8];
       if constexpr (EPI) {
         if (sp.Z) {
-          const uint4* zrow = reinterpret_cast<const uint4*>(static_cast<const T16*>(sp.Z) + y_bi * sp.zs[0] +
-                                                              (int64_t)(y_t0 + l) * sp.zs[1] + y_hi * sp.zs[2]);
+          const T16* zbase = static_cast<const T16*>(sp.Z) + y_bi * sp.zs[0] + y_hi * sp.zs[2] + 8 * (lane & 7);
 #pragma unroll
-          for (int c = 0; c < 8; ++c) zr[c] = __ldg(zrow + c);
+          for (int i = 0; i < 8; ++i) {
+            const int row = lane_base + 4 * i + (lane >> 3);
+            zr[i] = __ldg(reinterpret_cast<const uint4*>(zbase + (int64_t)(y_t0 + row) * sp.zs[1]));
+          }
         }
       }
       if (!cwait(&m->bar_y[h], y_it & 1, STATUS_WAIT_TIMEOUT_MMA)) return false;
@@ -531,29 +535,46 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         if constexpr (EPI) {
           // Y <- (Y + x * D) * silu(z) (model_ref.py:116-118) in fp32; x is this thread's row of the X tile, still in
           // the stage that the Y rows go to; silu(z) = z * (0.5 + 0.5 tanh(z / 2)), the tanh on 16-bit pairs.
-          const float dskip = sp.D ? sp.D[y_hi] : 0.f;
           const bool gate = sp.Z != nullptr;
-          const uint32_t half2 = pack2<T16>(0.5f, 0.5f);
+          if (sp.D) {
+            const float dskip = sp.D[y_hi];
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            const uint4 xr = lds128(ystage + l * 128 + ((c ^ swz) << 4));
-            const uint32_t xw[4] = {xr.x, xr.y, xr.z, xr.w};
-            const uint32_t zw[4] = {zr[c].x, zr[c].y, zr[c].z, zr[c].w};
+            for (int c = 0; c < 8; ++c) {
+              const uint4 xr = lds128(ystage + l * 128 + ((c ^ swz) << 4));
+              const uint32_t xw[4] = {xr.x, xr.y, xr.z, xr.w};
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              uint32_t* yy = (c < 4) ? &y0[8 * c + 2 * e] : &y1[8 * (c - 4) + 2 * e];
-              float v0 = __uint_as_float(yy[0]), v1 = __uint_as_float(yy[1]);
-              const float2 xf = unpack2<T16>(xw[e]);
-              v0 = fmaf(xf.x, dskip, v0);
-              v1 = fmaf(xf.y, dskip, v1);
-              if (gate) {
-                const float2 zf = unpack2<T16>(zw[e]);
-                const float2 th = unpack2<T16>(tanh2<T16>(mul2<T16>(zw[e], half2)));
-                v0 *= zf.x * fmaf(0.5f, th.x, 0.5f);
-                v1 *= zf.y * fmaf(0.5f, th.y, 0.5f);
+              for (int e = 0; e < 4; ++e) {
+                uint32_t* yy = (c < 4) ? &y0[8 * c + 2 * e] : &y1[8 * (c - 4) + 2 * e];
+                const float2 xf = unpack2<T16>(xw[e]);
+                yy[0] = __float_as_uint(fmaf(xf.x, dskip, __uint_as_float(yy[0])));
+                yy[1] = __float_as_uint(fmaf(xf.y, dskip, __uint_as_float(yy[1])));
               }
-              yy[0] = __float_as_uint(v0);
-              yy[1] = __float_as_uint(v1);
+            }
+          }
+          if (gate) {
+            // x is consumed: the warp's gate rows go through its 32 rows of the stage to the threads that own them
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int row = lane_base + 4 * i + (lane >> 3);
+              sts128(ystage + row * 128 + ((((uint32_t)lane & 7u) ^ ((uint32_t)row & 7u)) << 4), zr[i]);
+            }
+            __syncwarp();
+            const uint32_t half2 = pack2<T16>(0.5f, 0.5f);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              const uint4 zq = lds128(ystage + l * 128 + ((c ^ swz) << 4));
+              const uint32_t zw[4] = {zq.x, zq.y, zq.z, zq.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                uint32_t* yy = (c < 4) ? &y0[8 * c + 2 * e] : &y1[8 * (c - 4) + 2 * e];
+                // silu(z) = z * (0.5 + 0.5 tanh(z / 2)) on the packed 16-bit pair, as the reference forms it in
+                // half precision (model_ref.py:118); the product with Y is taken in fp32
+                const uint32_t sg = fma2<T16>(tanh2<T16>(mul2<T16>(zw[e], half2)), half2, half2);
+                const float2 gf = unpack2<T16>(mul2<T16>(zw[e], sg));
+                yy[0] = __float_as_uint(__uint_as_float(yy[0]) * gf.x);
+                yy[1] = __float_as_uint(__uint_as_float(yy[1]) * gf.y);
+              }
             }
           }
         }

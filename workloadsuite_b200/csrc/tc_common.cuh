@@ -44,6 +44,22 @@ __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// Packed 16-bit fused multiply-add a * b + c.
+template <typename T16>
+__device__ __forceinline__ uint32_t fma2(uint32_t a, uint32_t b, uint32_t c);
+template <>
+__device__ __forceinline__ uint32_t fma2<__nv_bfloat16>(uint32_t a, uint32_t b, uint32_t c) {
+  __nv_bfloat162 r = __hfma2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b),
+                             *reinterpret_cast<const __nv_bfloat162*>(&c));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+template <>
+__device__ __forceinline__ uint32_t fma2<__half>(uint32_t a, uint32_t b, uint32_t c) {
+  __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b),
+                      *reinterpret_cast<const __half2*>(&c));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
 // tanh of a packed pair of 16-bit values (one MUFU operation for the pair)
 template <typename T16>
 __device__ __forceinline__ uint32_t tanh2(uint32_t v);

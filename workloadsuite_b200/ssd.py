@@ -146,6 +146,7 @@ def ssd_forward(
     reuse_segments: bool = False,
     D: Optional[torch.Tensor] = None,
     z: Optional[torch.Tensor] = None,
+    separate_epilogue: bool = False,
 ):
     """Mamba-2 SSD forward ``Y = SSD(X, A, B, C)`` on the current CUDA stream.
 
@@ -161,6 +162,7 @@ def ssd_forward(
     ``D`` [h] and ``z`` [b,s,h,p] (dtype of X) add the layer's skip and gate to the kernel's epilogue:
     ``Y <- (Y + X * D[head]) * silu(z)`` (``model_ref.py:116-118``), evaluated in float32 and rounded once;
     either may be given alone.  Note that the skip term uses ``X`` as passed, i.e. before ``dt``.
+    ``separate_epilogue`` runs them as a kernel of their own even where the main kernel could fuse them.
 
     Returns Y [b,s,h,p] in X's dtype, plus the float32 final state [b,h,n,p] and/or
     the summed log-decay [b,h] when asked.  With ``state_only`` no Y is produced.
@@ -193,6 +195,8 @@ def ssd_forward(
     args = _lib.SsdArgs()
     _fill(args, X, A, B, C_, dt, initial_states, Y, final_state, final_ld, chunk, kernel, nsegments, state_only,
           reuse_segments)
+    if separate_epilogue:
+        args.flags |= _lib.FLAG_SEPARATE_EPILOGUE
     if D is not None:
         args.D = D.data_ptr()
     if z is not None:
