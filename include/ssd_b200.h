@@ -147,6 +147,18 @@ int ssd_b200_fold_states(const float* states, int64_t states_shard_stride, const
                          int64_t logdecay_shard_stride, const float* initial, float* out, int32_t nshards,
                          int32_t rank, int64_t units, int64_t np, void* stream);
 
+/* Causal depthwise conv1d + SiLU, the producer of the core's X: replaces
+ *   x = silu(conv1d(x.transpose)[..., :seq_len]).transpose     model_ref.py:83-86
+ * (nn.Conv1d(d, d, taps, padding=taps-1, groups=d, bias) of model_ref.py:50-58) without the two
+ * transposes:  y[b,t,c] = silu(bias[c] + sum_k weight[c,k] * x[b, t-(taps-1)+k, c]), zeros before t = 0.
+ * x and y are [batch, seqlen, channels] with the channel axis contiguous and the given element strides
+ * for batch and sequence (x may be a column slice of the projection output); weight is [channels, taps]
+ * (the [d,1,taps] parameter), bias [channels] or NULL; all in `dtype`; fp32 accumulation, one rounding.
+ * channels % 8 == 0, taps in 2..4. */
+int ssd_b200_conv1d_silu(const void* x, const void* weight, const void* bias, void* y, int32_t batch,
+                         int32_t seqlen, int32_t channels, int32_t taps, int32_t dtype, int64_t x_stride_b,
+                         int64_t x_stride_l, int64_t y_stride_b, int64_t y_stride_l, void* stream);
+
 /* Whole forward with HOST buffers: copies X/A/B/C (and dt, initial_state when
  * given) from host memory, runs the forward and copies Y (and final_state) back,
  * pipelined over batch slices on internal streams.  Every pointer in `host` is a

@@ -200,8 +200,7 @@ def ssd_layer_pre(layer, u: torch.Tensor):
     zxbcdt = layer.in_proj(u)                                                # :75
     gn = layer.n_groups * layer.d_state
     x, z, B, C, dt = torch.split(zxbcdt, [layer.d_inner, layer.d_inner, gn, gn, layer.n_heads], dim=-1)  # :76
-    x = layer.conv1d(x.transpose(1, 2))[..., :seq_len]                       # :83-84
-    x = F.silu(x).transpose(1, 2)                                            # :85-86
+    x = causal_conv1d_silu(x, layer.conv1d.weight, layer.conv1d.bias)        # :83-86
     x = x.reshape(batch, seq_len, layer.n_heads, layer.d_head)               # :89
     B = B.reshape(batch, seq_len, layer.n_groups, layer.d_state)             # :90
     C = C.reshape(batch, seq_len, layer.n_groups, layer.d_state)             # :91
@@ -209,6 +208,20 @@ def ssd_layer_pre(layer, u: torch.Tensor):
     A = -torch.exp(layer.A_log)                                              # :102
     A_dt = A * dt.float()                                                    # :103
     return x, z, B, C, dt, A_dt
+
+
+def causal_conv1d_silu(x: torch.Tensor, weight: torch.Tensor, bias=None, dtype=None) -> torch.Tensor:
+    """Causal depthwise conv + SiLU of ``SSDLayer.forward`` (``model_ref.py:83-86`` with the ``nn.Conv1d`` of
+    ``:50-58``): x [b,l,d], weight [d,1,k], bias [d]; the same operator calls as the reference, in ``dtype``
+    (default: x's dtype; ``torch.float64`` for an exact reference).  Returns [b,l,d]."""
+    import torch.nn.functional as F
+
+    dtype = dtype or x.dtype
+    d, k = weight.shape[0], weight.shape[-1]
+    xt = x.to(dtype).transpose(1, 2)                                          # :83
+    y = F.conv1d(xt, weight.to(dtype).reshape(d, 1, k), None if bias is None else bias.to(dtype),
+                 padding=k - 1, groups=d)[..., : x.shape[1]]                  # :84
+    return F.silu(y).transpose(1, 2)                                          # :85-86
 
 
 def ssd_epilogue(Y: torch.Tensor, x: torch.Tensor, D=None, z=None, dtype=None) -> torch.Tensor:

@@ -375,6 +375,29 @@ def test_skip_and_gate_epilogue(case):
     assert per_bh < TOL[dtype] and fro < TOL[dtype], (case, per_bh, fro)
 
 
+@pytest.mark.parametrize("dtype,taps,sliced", [(torch.float16, 4, True), (torch.bfloat16, 4, False), (torch.float32, 3, True),
+                                               (torch.float16, 2, False)])
+def test_causal_conv1d_silu(dtype, taps, sliced):
+    """The X producer (``model_ref.py:83-86``): CUDA kernel against the reference's operator calls in fp64; the input
+    may be a column slice of a wider projection output, ragged last token chunk included."""
+    W = _ssd()
+    gen = torch.Generator().manual_seed(300 + taps)
+    b, l, d = 3, 200, 192
+    wide = torch.randn(b, l, d + 72, generator=gen).to(dtype)
+    x = wide[..., 8:8 + d] if sliced else wide[..., :d].contiguous()
+    weight = (torch.randn(d, 1, taps, generator=gen) * 0.5).to(dtype)
+    bias = torch.randn(d, generator=gen).to(dtype)
+    y = W.conv1d_silu(x.to(DEV) if not sliced else wide.to(DEV)[..., 8:8 + d], weight.to(DEV), bias.to(DEV))
+    torch.cuda.synchronize()
+    ref = O.causal_conv1d_silu(x, weight, bias, dtype=torch.float64)
+    err = (y.cpu().double() - ref).abs().max().item() / ref.abs().max().item()
+    assert y.shape == (b, l, d) and y.is_contiguous()
+    assert err < (1e-5 if dtype == torch.float32 else 5e-3), err
+    y2 = W.conv1d_silu(x.to(DEV).contiguous(), weight.to(DEV), None)
+    ref2 = O.causal_conv1d_silu(x, weight, None, dtype=torch.float64)
+    assert (y2.cpu().double() - ref2).abs().max().item() / ref2.abs().max().item() < (1e-5 if dtype == torch.float32 else 5e-3)
+
+
 def test_host_buffer_forward_equals_device_forward():
     W = _ssd()
     inp = O.make_inputs(b=3, s=512, h=8, p=64, n=64, g=2, dtype=torch.bfloat16, init=True, seed=13, decay_scale=0.1)

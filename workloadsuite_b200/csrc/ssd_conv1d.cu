@@ -1,0 +1,138 @@
+// Causal depthwise conv1d + SiLU, the producer of the SSD core's X (model_ref.py:50-58, 83-86):
+//   y[b,t,c] = silu(bias[c] + sum_{k<K} w[c,k] * x[b, t-(K-1)+k, c]),  x == 0 before the sequence start
+// (nn.Conv1d(d, d, K, padding=K-1, groups=d) on [b,d,l], output truncated to the first l steps).
+// The reference transposes to [b,d,l] and back; here x stays channel-innermost, read as a strided view of
+// the projection output and written in the [b,l,h*p] layout the core reads.  HBM-bound: every x read once.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdint>
+
+#include "ssd_b200.h"
+#include "ssd_common.cuh"
+
+namespace ssd {
+namespace {
+
+constexpr int kTokensPerThread = 32;
+constexpr int kMaxTaps = 8;
+
+// One thread: 8 consecutive channels (one 16-byte vector of a 16-bit row), kTokensPerThread consecutive tokens,
+// the last K-1 rows kept in registers as a sliding window.
+template <typename T, int K>
+__global__ void __launch_bounds__(128)
+conv1d_silu_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ bias, T* __restrict__ y,
+                   int batch, int seqlen, int channels, int64_t xsb, int64_t xsl, int64_t ysb, int64_t ysl, int vec_ok) {
+  const int cvecs = channels / 8;
+  const int chunks = (seqlen + kTokensPerThread - 1) / kTokensPerThread;
+  const int64_t total = (int64_t)batch * chunks * cvecs;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int cv = (int)(i % cvecs);          // consecutive threads: consecutive channel vectors (coalesced rows)
+  const int64_t r = i / cvecs;
+  const int ch = (int)(r % chunks);
+  const int b = (int)(r / chunks);
+  const int c0 = 8 * cv;
+  const int t_begin = ch * kTokensPerThread, t_end = min(seqlen, t_begin + kTokensPerThread);
+
+  float wk[K][8], bs[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    bs[e] = bias ? Cvt<T>::to_f(bias[c0 + e]) : 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) wk[k][e] = Cvt<T>::to_f(w[(int64_t)(c0 + e) * K + k]);
+  }
+  auto load_row = [&](int t, float (&v)[8]) {
+    if (t < 0) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = 0.f;
+      return;
+    }
+    const T* p = x + b * xsb + (int64_t)t * xsl + c0;
+    alignas(16) T raw[8];
+    if (vec_ok && sizeof(T) == 2) {
+      *reinterpret_cast<uint4*>(raw) = *reinterpret_cast<const uint4*>(p);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) raw[e] = p[e];
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = Cvt<T>::to_f(raw[e]);
+  };
+
+  float win[K][8];   // win[k] = row t-(K-1)+k
+#pragma unroll
+  for (int k = 0; k < K - 1; ++k) load_row(t_begin - (K - 1) + k, win[k + 1]);
+  for (int t = t_begin; t < t_end; ++t) {
+#pragma unroll
+    for (int k = 0; k < K - 1; ++k) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) win[k][e] = win[k + 1][e];
+    }
+    load_row(t, win[K - 1]);
+    alignas(16) T out[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float acc = bs[e];
+#pragma unroll
+      for (int k = 0; k < K; ++k) acc = fmaf(wk[k][e], win[k][e], acc);
+      out[e] = Cvt<T>::from_f(acc / (1.f + __expf(-acc)));
+    }
+    T* q = y + b * ysb + (int64_t)t * ysl + c0;
+    if (vec_ok && sizeof(T) == 2) {
+      *reinterpret_cast<uint4*>(q) = *reinterpret_cast<const uint4*>(out);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) q[e] = out[e];
+    }
+  }
+}
+
+template <typename T>
+int launch_conv(const void* x, const void* w, const void* bias, void* y, int batch, int seqlen, int channels, int taps,
+                int64_t xsb, int64_t xsl, int64_t ysb, int64_t ysl, cudaStream_t stream) {
+  const int chunks = (seqlen + kTokensPerThread - 1) / kTokensPerThread;
+  const int64_t total = (int64_t)batch * chunks * (channels / 8);
+  if ((total + 127) / 128 > 0x7fffffffLL) return SSD_ERR_TOO_LARGE;
+  const unsigned grid = (unsigned)((total + 127) / 128);
+  const bool al = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0 && xsb % 8 == 0 &&
+                  xsl % 8 == 0 && ysb % 8 == 0 && ysl % 8 == 0;
+  const T* xx = static_cast<const T*>(x);
+  const T* ww = static_cast<const T*>(w);
+  const T* bb = static_cast<const T*>(bias);
+  T* yy = static_cast<T*>(y);
+  switch (taps) {
+    case 2: conv1d_silu_kernel<T, 2><<<grid, 128, 0, stream>>>(xx, ww, bb, yy, batch, seqlen, channels, xsb, xsl, ysb, ysl, al); break;
+    case 3: conv1d_silu_kernel<T, 3><<<grid, 128, 0, stream>>>(xx, ww, bb, yy, batch, seqlen, channels, xsb, xsl, ysb, ysl, al); break;
+    case 4: conv1d_silu_kernel<T, 4><<<grid, 128, 0, stream>>>(xx, ww, bb, yy, batch, seqlen, channels, xsb, xsl, ysb, ysl, al); break;
+    default: return SSD_ERR_UNSUPPORTED;
+  }
+  return cudaGetLastError() == cudaSuccess ? SSD_OK : SSD_ERR_CUDA;
+}
+
+}  // namespace
+}  // namespace ssd
+
+extern "C" int ssd_b200_conv1d_silu(const void* x, const void* weight, const void* bias, void* y, int32_t batch,
+                                    int32_t seqlen, int32_t channels, int32_t taps, int32_t dtype, int64_t x_stride_b,
+                                    int64_t x_stride_l, int64_t y_stride_b, int64_t y_stride_l, void* stream) {
+  if (!x || !weight || !y) return SSD_ERR_NULL_POINTER;
+  if (batch <= 0 || seqlen <= 0 || channels <= 0 || taps <= 0 || taps > ssd::kMaxTaps) return SSD_ERR_BAD_SHAPE;
+  if (channels % 8 != 0) return SSD_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case SSD_DTYPE_F32:
+      return ssd::launch_conv<float>(x, weight, bias, y, batch, seqlen, channels, taps, x_stride_b, x_stride_l,
+                                     y_stride_b, y_stride_l, s);
+    case SSD_DTYPE_F16:
+      return ssd::launch_conv<__half>(x, weight, bias, y, batch, seqlen, channels, taps, x_stride_b, x_stride_l,
+                                      y_stride_b, y_stride_l, s);
+    case SSD_DTYPE_BF16:
+      return ssd::launch_conv<__nv_bfloat16>(x, weight, bias, y, batch, seqlen, channels, taps, x_stride_b,
+                                             x_stride_l, y_stride_b, y_stride_l, s);
+    default:
+      return SSD_ERR_UNSUPPORTED;
+  }
+}

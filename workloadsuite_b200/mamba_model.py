@@ -24,7 +24,12 @@ _PKG_PARENT = str(Path(__file__).resolve().parent.parent)
 if _PKG_PARENT not in sys.path:
     sys.path.insert(0, _PKG_PARENT)
 
-from workloadsuite_b200.ssd import ssd_forward  # noqa: E402
+from workloadsuite_b200.ssd import conv1d_silu, ssd_forward  # noqa: E402
+
+
+@torch.compiler.disable
+def _conv(x, weight, bias):
+    return conv1d_silu(x, weight, bias)
 
 
 @torch.compiler.disable
@@ -75,9 +80,8 @@ class SSDLayer(nn.Module):
         gn = self.n_groups * self.d_state
         x, z, B, C, dt = torch.split(zxbcdt, [self.d_inner, self.d_inner, gn, gn, self.n_heads], dim=-1)
 
-        x = self.conv1d(x.transpose(1, 2))[..., :seq_len]
-        x = F.silu(x).transpose(1, 2).contiguous()          # [b, l, d_inner], channel-contiguous
-        x = x.view(batch, seq_len, self.n_heads, self.d_head)
+        # causal depthwise conv + SiLU (model_ref.py:83-86) straight from the projection's columns, no transposes
+        x = _conv(x, self.conv1d.weight, self.conv1d.bias).view(batch, seq_len, self.n_heads, self.d_head)
         B = _tma_friendly(B.unflatten(-1, (self.n_groups, self.d_state)))   # ungrouped: no GQA repeat
         C = _tma_friendly(C.unflatten(-1, (self.n_groups, self.d_state)))
 

@@ -218,6 +218,39 @@ def ssd_forward(
     return outs[0] if len(outs) == 1 else tuple(outs)
 
 
+def conv1d_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal depthwise conv1d + SiLU on the current CUDA stream: ``silu(conv1d(x^T)[..., :l])^T`` of
+    ``model_ref.py:83-86`` without the transposes.
+
+    x [b,l,d] with a contiguous channel axis (a column slice of the projection output is fine); weight the
+    ``nn.Conv1d(d, d, k, groups=d)`` parameter [d,1,k] (or [d,k]); bias [d] or None.  Returns [b,l,d] contiguous
+    in x's dtype (fp32 accumulation, one rounding).
+    """
+    if not x.is_cuda:
+        raise RuntimeError("conv1d_silu needs CUDA tensors (there is no CPU path)")
+    if x.dim() != 3 or x.stride(2) != 1 or x.dtype not in _DTYPES:
+        raise ValueError("x must be [b,l,d] float32/float16/bfloat16 with a contiguous channel axis")
+    b, l, d = x.shape
+    w = weight.reshape(d, -1).to(x.dtype).contiguous()
+    taps = w.shape[1]
+    if bias is not None:
+        bias = bias.to(x.dtype).contiguous()
+    if out is None:
+        out = torch.empty((b, l, d), dtype=x.dtype, device=x.device)
+    elif out.shape != x.shape or out.dtype != x.dtype or out.stride(2) != 1:
+        raise ValueError("out must be [b,l,d] in the dtype of x with a contiguous channel axis")
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        rc = lib.ssd_b200_conv1d_silu(x.data_ptr(), w.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                      out.data_ptr(), b, l, d, taps, _DTYPES[x.dtype], x.stride(0), x.stride(1),
+                                      out.stride(0), out.stride(1),
+                                      C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream))
+    if rc != _lib.SSD_OK:
+        _raise(rc)
+    return out
+
+
 def kernel_name(X, A, B, C_, chunk, kernel=None) -> str:
     """Which kernel family ``ssd_forward`` would run for these tensors."""
     _check(X, A, B, C_, None, None)
