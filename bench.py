@@ -463,6 +463,52 @@ def main():
         except Exception as exc:
             others[args.workload + "+skip_gate"] = {"error": f"{type(exc).__name__}: {exc}"}
 
+        # The X producer of the same workload: causal depthwise conv1d(k=4) + SiLU (model_ref.py:83-86) over
+        # [b, s, h*p], read as a column slice of a projection-sized buffer; bytes = one read + one write.
+        try:
+            c = CONFIGS[args.workload]
+            dch = c["h"] * c["p"]
+            wdt = torch.bfloat16 if c["dtype"] == "bf16" else (torch.float16 if c["dtype"] == "f16" else torch.float32)
+            wide = [torch.randn(c["b"], c["s"], 2 * dch + 64, device=dev, dtype=wdt) for _ in range(2)]
+            yo = [torch.empty(c["b"], c["s"], dch, device=dev, dtype=wdt) for _ in range(2)]
+            cw = torch.randn(dch, 1, 4, device=dev, dtype=wdt)
+            cb = torch.randn(dch, device=dev, dtype=wdt)
+
+            def st_conv(i):
+                W.conv1d_silu(wide[i][..., :dch], cw, cb, out=yo[i])
+
+            ms_c, _, _ = time_steps(st_conv, 2, max(5, args.steps // 2), 3, False)
+            cbytes = 2 * c["b"] * c["s"] * dch * wide[0].element_size()
+            others[args.workload + ":conv1d_silu"] = {"ms_per_step": ms_c, "GBps": cbytes / (ms_c * 1e-3) / 1e9,
+                                                      "hbm_frac_of_measured": cbytes / (ms_c * 1e-3) / 1e9 / peak}
+            del wide, yo
+            torch.cuda.empty_cache()
+        except Exception as exc:
+            others[args.workload + ":conv1d_silu"] = {"error": f"{type(exc).__name__}: {exc}"}
+
+        # The drop-in Model (reference contract: Model / get_init_inputs / get_inputs, model_ref.py:165-229) at the
+        # reference's production layer shape, two layers instead of 24: projections on cuBLAS, conv, core, skip and gate
+        # on this library's kernels.
+        try:
+            from workloadsuite_b200 import mamba_model as MM
+            init = MM.get_init_inputs()
+            init[1] = 2
+            model = MM.Model(*init).to(dev).eval()
+            xin = [torch.randn(MM.batch_size, MM.seq_length, MM.d_model, device=dev, dtype=torch.float16) for _ in range(2)]
+
+            def st_model(i):
+                with torch.inference_mode():
+                    model(xin[i])
+
+            ms_m, _, _ = time_steps(st_model, 2, max(5, args.steps // 5), 3, False)
+            others["mamba_model_2_layers"] = {"ms_per_step": ms_m, "ms_per_layer": ms_m / 2,
+                                              "tokens_per_s": MM.batch_size * MM.seq_length / (ms_m * 1e-3),
+                                              "shape": "b8 s2048 d_model2048 h128 p64 n128 g8 block64 fp16"}
+            del model, xin
+            torch.cuda.empty_cache()
+        except Exception as exc:
+            others["mamba_model_2_layers"] = {"error": f"{type(exc).__name__}: {exc}"}
+
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:

@@ -16,13 +16,70 @@
 namespace ssd {
 namespace {
 
-constexpr int kTokensPerThread = 32;
+constexpr int kTokensPerThread = 64;
 constexpr int kMaxTaps = 8;
+
+// 8 consecutive elements <-> 8 floats, through 16-byte vectors kept in registers when `vec`.
+__device__ __forceinline__ float2 up2(const __half*, uint32_t v) { return __half22float2(*reinterpret_cast<const __half2*>(&v)); }
+__device__ __forceinline__ float2 up2(const __nv_bfloat16*, uint32_t v) {
+  return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+}
+__device__ __forceinline__ float2 up2(const float*, uint32_t) { return make_float2(0.f, 0.f); }   // (never taken)
+__device__ __forceinline__ uint32_t pk2(const __half*, float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t pk2(const __nv_bfloat16*, float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&v)[8], bool vec) {
+  if (vec) {
+    const uint4 q = *reinterpret_cast<const uint4*>(p);
+    const float2 a = up2(p, q.x), b = up2(p, q.y), c = up2(p, q.z), d = up2(p, q.w);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = Cvt<T>::to_f(p[e]);
+  }
+}
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&v)[8], bool vec) {
+  if (vec) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = p[e];
+  }
+}
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float (&v)[8], bool vec) {
+  if (vec) {
+    uint4 q;
+    q.x = pk2(p, v[0], v[1]); q.y = pk2(p, v[2], v[3]); q.z = pk2(p, v[4], v[5]); q.w = pk2(p, v[6], v[7]);
+    *reinterpret_cast<uint4*>(p) = q;
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) p[e] = Cvt<T>::from_f(v[e]);
+  }
+}
+template <>
+__device__ __forceinline__ void store8<float>(float* p, const float (&v)[8], bool vec) {
+  if (vec) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) p[e] = v[e];
+  }
+}
 
 // One thread: 8 consecutive channels (one 16-byte vector of a 16-bit row), kTokensPerThread consecutive tokens,
 // the last K-1 rows kept in registers as a sliding window.
 template <typename T, int K>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 4)
 conv1d_silu_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ bias, T* __restrict__ y,
                    int batch, int seqlen, int channels, int64_t xsb, int64_t xsl, int64_t ysb, int64_t ysl, int vec_ok) {
   const int cvecs = channels / 8;
@@ -44,48 +101,63 @@ conv1d_silu_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __
 #pragma unroll
     for (int k = 0; k < K; ++k) wk[k][e] = Cvt<T>::to_f(w[(int64_t)(c0 + e) * K + k]);
   }
-  auto load_row = [&](int t, float (&v)[8]) {
-    if (t < 0) {
+  const bool vec = vec_ok != 0;
+  auto load_row = [&](int t, float (&v)[8]) {   // zeros outside the sequence
+    if (t < 0 || t >= seqlen) {
 #pragma unroll
       for (int e = 0; e < 8; ++e) v[e] = 0.f;
-      return;
-    }
-    const T* p = x + b * xsb + (int64_t)t * xsl + c0;
-    alignas(16) T raw[8];
-    if (vec_ok && sizeof(T) == 2) {
-      *reinterpret_cast<uint4*>(raw) = *reinterpret_cast<const uint4*>(p);
     } else {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) raw[e] = p[e];
+      load8<T>(x + b * xsb + (int64_t)t * xsl + c0, v, vec);
     }
-#pragma unroll
-    for (int e = 0; e < 8; ++e) v[e] = Cvt<T>::to_f(raw[e]);
   };
-
-  float win[K][8];   // win[k] = row t-(K-1)+k
-#pragma unroll
-  for (int k = 0; k < K - 1; ++k) load_row(t_begin - (K - 1) + k, win[k + 1]);
-  for (int t = t_begin; t < t_end; ++t) {
-#pragma unroll
-    for (int k = 0; k < K - 1; ++k) {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) win[k][e] = win[k + 1][e];
-    }
-    load_row(t, win[K - 1]);
-    alignas(16) T out[8];
+  auto emit = [&](int t, float (&win)[K][8]) {   // win holds rows t-(K-1) .. t
+    float out[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       float acc = bs[e];
 #pragma unroll
       for (int k = 0; k < K; ++k) acc = fmaf(wk[k][e], win[k][e], acc);
-      out[e] = Cvt<T>::from_f(acc / (1.f + __expf(-acc)));
+      out[e] = __fdividef(acc, 1.f + __expf(-acc));
     }
-    T* q = y + b * ysb + (int64_t)t * ysl + c0;
-    if (vec_ok && sizeof(T) == 2) {
-      *reinterpret_cast<uint4*>(q) = *reinterpret_cast<const uint4*>(out);
-    } else {
+    store8<T>(y + b * ysb + (int64_t)t * ysl + c0, out, vec);
+  };
+
+  float win[K][8];   // win[k] = row t-(K-1)+k
 #pragma unroll
-      for (int e = 0; e < 8; ++e) q[e] = out[e];
+  for (int k = 0; k < K - 1; ++k) load_row(t_begin - (K - 1) + k, win[k + 1]);
+  if (vec && sizeof(T) == 2) {
+    // rows fetched four at a time as raw 16-byte vectors: several loads per thread in flight, few registers
+    constexpr int kBatch = 4;
+    const T* xrow = x + b * xsb + c0;
+    for (int t0 = t_begin; t0 < t_end; t0 += kBatch) {
+      uint4 raw[kBatch];
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u)
+        raw[u] = (t0 + u < t_end) ? *reinterpret_cast<const uint4*>(xrow + (int64_t)(t0 + u) * xsl) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        if (t0 + u < t_end) {
+#pragma unroll
+          for (int k = 0; k < K - 1; ++k) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) win[k][e] = win[k + 1][e];
+          }
+          const float2 a = up2(xrow, raw[u].x), bq = up2(xrow, raw[u].y), c = up2(xrow, raw[u].z), d = up2(xrow, raw[u].w);
+          win[K - 1][0] = a.x; win[K - 1][1] = a.y; win[K - 1][2] = bq.x; win[K - 1][3] = bq.y;
+          win[K - 1][4] = c.x; win[K - 1][5] = c.y; win[K - 1][6] = d.x; win[K - 1][7] = d.y;
+          emit(t0 + u, win);
+        }
+      }
+    }
+  } else {
+    for (int t = t_begin; t < t_end; ++t) {
+#pragma unroll
+      for (int k = 0; k < K - 1; ++k) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) win[k][e] = win[k + 1][e];
+      }
+      load_row(t, win[K - 1]);
+      emit(t, win);
     }
   }
 }
@@ -97,8 +169,9 @@ int launch_conv(const void* x, const void* w, const void* bias, void* y, int bat
   const int64_t total = (int64_t)batch * chunks * (channels / 8);
   if ((total + 127) / 128 > 0x7fffffffLL) return SSD_ERR_TOO_LARGE;
   const unsigned grid = (unsigned)((total + 127) / 128);
-  const bool al = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0 && xsb % 8 == 0 &&
-                  xsl % 8 == 0 && ysb % 8 == 0 && ysl % 8 == 0;
+  const int per16 = 16 / (int)sizeof(T);
+  const bool al = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0 && xsb % per16 == 0 &&
+                  xsl % per16 == 0 && ysb % per16 == 0 && ysl % per16 == 0;
   const T* xx = static_cast<const T*>(x);
   const T* ww = static_cast<const T*>(w);
   const T* bb = static_cast<const T*>(bias);
