@@ -52,7 +52,7 @@ L2_BYTES = 126e6
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu capture summarised
 # in profiles/ssd_tc2_kernel_cfg2.md (same command line as this bench, --steps 2 --warmup 3); None where no capture
 # of that (workload, kernel, world size) exists.
-NCU_TRAFFIC_BYTES = {("cfg2", "tcgen05", 1): 666.3e6}
+NCU_TRAFFIC_BYTES = {("cfg2", "tcgen05", 1): 666.1e6}
 
 
 def algorithmic_bytes(cfg, h=None, s=None):

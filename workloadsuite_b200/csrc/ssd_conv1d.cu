@@ -16,7 +16,7 @@
 namespace ssd {
 namespace {
 
-constexpr int kTokensPerThread = 64;
+constexpr int kTokensPerThread = 32;
 constexpr int kMaxTaps = 8;
 
 // 8 consecutive elements <-> 8 floats, through 16-byte vectors kept in registers when `vec`.
@@ -117,7 +117,14 @@ conv1d_silu_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __
       float acc = bs[e];
 #pragma unroll
       for (int k = 0; k < K; ++k) acc = fmaf(wk[k][e], win[k][e], acc);
-      out[e] = __fdividef(acc, 1.f + __expf(-acc));
+      if (sizeof(T) == 2) {
+        // silu(a) = a * (0.5 + 0.5 tanh(a / 2)): one MUFU operation; its 2^-11 error is below the 16-bit rounding
+        float th;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * acc));
+        out[e] = acc * fmaf(0.5f, th, 0.5f);
+      } else {
+        out[e] = __fdividef(acc, 1.f + __expf(-acc));
+      }
     }
     store8<T>(y + b * ysb + (int64_t)t * ysl + c0, out, vec);
   };
