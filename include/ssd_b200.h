@@ -159,6 +159,16 @@ int ssd_b200_conv1d_silu(const void* x, const void* weight, const void* bias, vo
                          int32_t seqlen, int32_t channels, int32_t taps, int32_t dtype, int64_t x_stride_b,
                          int64_t x_stride_l, int64_t y_stride_b, int64_t y_stride_l, void* stream);
 
+/* dt discretisation ahead of the core: replaces
+ *   dt = softplus(dt + dt_bias); A_dt = -exp(A_log) * dt.float()      model_ref.py:94, 102-103
+ * dt_raw is [batch, seqlen, nheads] in `dtype` with the head axis contiguous and the given element strides
+ * (a column slice of the projection output), dt_bias [nheads] in `dtype` or NULL, A_log [nheads] fp32.
+ * Writes dt_out [batch, seqlen, nheads] in `dtype` and A_dt_out [batch, seqlen, nheads] fp32, both contiguous:
+ * the `dt` and `A` arguments of ssd_b200_forward. */
+int ssd_b200_dt_prologue(const void* dt_raw, int64_t stride_b, int64_t stride_l, const void* dt_bias,
+                         const float* A_log, void* dt_out, float* A_dt_out, int32_t batch, int32_t seqlen,
+                         int32_t nheads, int32_t dtype, void* stream);
+
 /* Whole forward with HOST buffers: copies X/A/B/C (and dt, initial_state when
  * given) from host memory, runs the forward and copies Y (and final_state) back,
  * pipelined over batch slices on internal streams.  Every pointer in `host` is a

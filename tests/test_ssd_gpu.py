@@ -398,6 +398,32 @@ def test_causal_conv1d_silu(dtype, taps, sliced):
     assert (y2.cpu().double() - ref2).abs().max().item() / ref2.abs().max().item() < (1e-5 if dtype == torch.float32 else 5e-3)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_dt_prologue(dtype):
+    """``softplus(dt + dt_bias)`` and ``A_dt = -exp(A_log) dt.float()`` (``model_ref.py:94, 102-103``) against the same
+    PyTorch operator calls on the CPU, from a column slice of a wider tensor."""
+    import torch.nn.functional as F
+
+    W = _ssd()
+    gen = torch.Generator().manual_seed(77)
+    b, l, h = 2, 300, 24
+    wide = (torch.randn(b, l, h + 40, generator=gen) * 3 - 2).to(dtype)
+    wide[0, 0, 8] = 30.0                                   # beyond softplus' linear threshold
+    bias = (torch.randn(h, generator=gen) - 2).to(dtype)
+    A_log = torch.log(torch.arange(1, h + 1, dtype=torch.float32))
+    dt, A_dt = W.dt_prologue(wide.to(DEV)[..., 8:8 + h], bias.to(DEV), A_log.to(DEV))
+    torch.cuda.synchronize()
+    dt_ref = F.softplus(wide[..., 8:8 + h].float() + bias.float()) if dtype == torch.float32 else \
+        F.softplus((wide[..., 8:8 + h] + bias).float()).to(dtype)
+    A_ref = -torch.exp(A_log) * dt_ref.float()
+    tol = 5e-6 if dtype == torch.float32 else 2 ** (-7 if dtype == torch.bfloat16 else -10)
+    assert dt.dtype == dtype and A_dt.dtype == torch.float32
+    assert ((dt.cpu().float() - dt_ref.float()).abs() / dt_ref.float().abs().clamp_min(1e-6)).max().item() < tol
+    assert ((A_dt.cpu() - A_ref).abs() / A_ref.abs().clamp_min(1e-6)).max().item() < tol
+    # A_dt is formed from the ROUNDED dt, as the reference does
+    assert torch.allclose(A_dt.cpu(), -torch.exp(A_log) * dt.cpu().float(), rtol=1e-6, atol=0)
+
+
 def test_host_buffer_forward_equals_device_forward():
     W = _ssd()
     inp = O.make_inputs(b=3, s=512, h=8, p=64, n=64, g=2, dtype=torch.bfloat16, init=True, seed=13, decay_scale=0.1)

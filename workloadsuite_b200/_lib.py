@@ -29,7 +29,7 @@ EXPORTS = (
     "ssd_b200_abi_version", "ssd_b200_strerror", "ssd_b200_workspace_bytes", "ssd_b200_kernel_name",
     "ssd_b200_forward", "ssd_b200_fold_states", "ssd_b200_host_scratch_bytes", "ssd_b200_forward_host",
     "ssd_b200_static_scratch_capacity", "ssd_b200_forward_static_scratch", "ssd_b200_plan",
-    "ssd_b200_conv1d_silu",
+    "ssd_b200_conv1d_silu", "ssd_b200_dt_prologue",
 )
 
 
@@ -93,6 +93,9 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     lib.ssd_b200_conv1d_silu.restype = C.c_int
     lib.ssd_b200_conv1d_silu.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                                          C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_void_p]
+    lib.ssd_b200_dt_prologue.restype = C.c_int
+    lib.ssd_b200_dt_prologue.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                         C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]
     got = lib.ssd_b200_abi_version()
     if got != ABI_VERSION:
         raise RuntimeError(f"libssd_b200 ABI version {got}, binding expects {ABI_VERSION}; rebuild the library")

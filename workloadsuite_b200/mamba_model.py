@@ -24,7 +24,12 @@ _PKG_PARENT = str(Path(__file__).resolve().parent.parent)
 if _PKG_PARENT not in sys.path:
     sys.path.insert(0, _PKG_PARENT)
 
-from workloadsuite_b200.ssd import conv1d_silu, ssd_forward  # noqa: E402
+from workloadsuite_b200.ssd import conv1d_silu, dt_prologue, ssd_forward  # noqa: E402
+
+
+@torch.compiler.disable
+def _dt(dt_raw, dt_bias, A_log):
+    return dt_prologue(dt_raw, dt_bias, A_log)
 
 
 @torch.compiler.disable
@@ -85,8 +90,7 @@ class SSDLayer(nn.Module):
         B = _tma_friendly(B.unflatten(-1, (self.n_groups, self.d_state)))   # ungrouped: no GQA repeat
         C = _tma_friendly(C.unflatten(-1, (self.n_groups, self.d_state)))
 
-        dt = F.softplus(dt + self.dt_bias)
-        A_dt = -torch.exp(self.A_log) * dt.float()
+        dt, A_dt = _dt(dt, self.dt_bias, self.A_log)      # softplus(dt + bias), -exp(A_log) dt   (model_ref.py:94, 102-103)
 
         z = _tma_friendly(z.unflatten(-1, (self.n_heads, self.d_head)))     # a view of the projection output
         Y = _core(x, A_dt, B, C, dt, self.block_len, self.D, z)             # (Y + x D) silu(z), model_ref.py:116-118

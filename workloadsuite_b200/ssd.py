@@ -251,6 +251,31 @@ def conv1d_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     return out
 
 
+def dt_prologue(dt_raw: torch.Tensor, dt_bias: Optional[torch.Tensor], A_log: torch.Tensor):
+    """``dt = softplus(dt_raw + dt_bias)`` and ``A_dt = -exp(A_log) * dt.float()`` (``model_ref.py:94, 102-103``) in one
+    pass on the current CUDA stream.  dt_raw [b,l,h] with a contiguous head axis (a column slice of the projection
+    output is fine); dt_bias [h] or None; A_log [h] float32.  Returns (dt [b,l,h] in dt_raw's dtype, A_dt float32)."""
+    if not dt_raw.is_cuda:
+        raise RuntimeError("dt_prologue needs CUDA tensors (there is no CPU path)")
+    if dt_raw.dim() != 3 or dt_raw.stride(2) != 1 or dt_raw.dtype not in _DTYPES:
+        raise ValueError("dt_raw must be [b,l,h] float32/float16/bfloat16 with a contiguous head axis")
+    b, l, h = dt_raw.shape
+    if dt_bias is not None:
+        dt_bias = dt_bias.to(dt_raw.dtype).contiguous()
+    A_log = A_log.to(device=dt_raw.device, dtype=torch.float32).contiguous()
+    dt = torch.empty((b, l, h), dtype=dt_raw.dtype, device=dt_raw.device)
+    A_dt = torch.empty((b, l, h), dtype=torch.float32, device=dt_raw.device)
+    lib = _lib.load()
+    with torch.cuda.device(dt_raw.device):
+        rc = lib.ssd_b200_dt_prologue(dt_raw.data_ptr(), dt_raw.stride(0), dt_raw.stride(1),
+                                      dt_bias.data_ptr() if dt_bias is not None else None, A_log.data_ptr(),
+                                      dt.data_ptr(), A_dt.data_ptr(), b, l, h, _DTYPES[dt_raw.dtype],
+                                      C.c_void_p(torch.cuda.current_stream(dt_raw.device).cuda_stream))
+    if rc != _lib.SSD_OK:
+        _raise(rc)
+    return dt, A_dt
+
+
 def kernel_name(X, A, B, C_, chunk, kernel=None) -> str:
     """Which kernel family ``ssd_forward`` would run for these tensors."""
     _check(X, A, B, C_, None, None)
