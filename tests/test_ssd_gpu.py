@@ -435,6 +435,23 @@ def test_host_buffer_forward_equals_device_forward():
     assert torch.equal(Yh, Yd.cpu())
 
 
+def test_host_buffer_forward_carries_the_state_across_sequence_chunks():
+    """A batch entry longer than one host chunk: the scan continues from chunk to chunk through the device-resident
+    state; initial and final states and the summed log-decay come through."""
+    W = _ssd()
+    inp = O.make_inputs(b=2, s=4096, h=16, p=64, n=128, g=2, dtype=torch.bfloat16, init=True, seed=14, decay_scale=0.02)
+    r = W.HostRunner(2, 4096, 16, 64, 128, 2, 256, torch.bfloat16, device=str(DEV))
+    out = torch.empty_like(inp["X"]).pin_memory()
+    fin = torch.empty(2, 16, 128, 64).pin_memory()
+    r.run(inp["X"].pin_memory(), inp["A"].pin_memory(), inp["B"].pin_memory(), inp["C"].pin_memory(), out,
+          initial_states=inp["initial_states"].pin_memory(), final_state=fin)
+    Yr, Hr = O.ssd_recurrence(inp["X"], inp["A"], inp["B"], inp["C"], initial_states=inp["initial_states"],
+                              return_final_state=True)
+    per_bh, fro = O.error_metrics(out, Yr)
+    assert per_bh < 2e-2 and fro < 2e-2, (per_bh, fro)
+    assert ((fin.double() - Hr).abs().max() / Hr.abs().max()).item() < 2e-2
+
+
 def test_dropin_model_matches_reference_golden(golden_dir):
     from workloadsuite_b200 import mamba_model as M
 

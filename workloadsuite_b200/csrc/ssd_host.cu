@@ -1,8 +1,11 @@
 // Host-buffer entry point: the SSD forward for callers whose tensors live in
-// host memory.  The (batch, head-block) slices of the problem are independent
-// scans, so the call is a three-stage pipeline over slices: host->device copy
-// of slice i+1, kernels of slice i and device->host copy of slice i-1 run on
-// three streams and overlap (PCIe is full duplex).
+// host memory.  Each batch entry is cut along the SEQUENCE into chunks of a few
+// thousand tokens: a chunk of X, Y, B, C, A, dt is one contiguous block of host
+// memory (plain 1-D copies at full PCIe rate), and the scan carries over from
+// chunk to chunk through the fp32 state, which stays on the device.  The call
+// is a three-stage pipeline over chunks: host->device copies of chunk i+1,
+// kernels of chunk i and device->host copy of chunk i-1 run on three streams
+// and overlap (PCIe is full duplex).
 #include <algorithm>
 #include <cstring>
 #include <vector>
@@ -11,16 +14,17 @@
 
 namespace {
 
-constexpr int kSlots = 3;
+constexpr int kSlots = 4;
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 int esize(int dtype) { return dtype == SSD_DTYPE_F32 ? 4 : 2; }
+int gcd_int(int a, int b) { return b == 0 ? a : gcd_int(b, a % b); }
 
 struct Plan {
-  int head_block;     // heads per slice
-  int groups_block;   // groups a slice touches (>= 1)
-  size_t x_bytes, a_bytes, y_bytes, dt_bytes, st_bytes, bc_bytes, ws_bytes, ld_bytes;
-  size_t slot_bytes, batch_bytes, total_bytes;
+  int tokens;      // tokens per chunk (the last chunk of a sequence may be shorter)
+  int nchunks;     // chunks per batch entry
+  size_t x_bytes, a_bytes, dt_bytes, bc_bytes, ws_bytes, ld_bytes, st_bytes;   // a, dt, bc: one whole batch entry
+  size_t slot_bytes, entry_bytes, total_bytes;
 };
 
 bool basic_ok(const SsdArgs* a) {
@@ -29,47 +33,50 @@ bool basic_ok(const SsdArgs* a) {
          (a->dtype == SSD_DTYPE_F32 || a->dtype == SSD_DTYPE_F16 || a->dtype == SSD_DTYPE_BF16);
 }
 
-void slice_args(const SsdArgs* a, int hb, SsdArgs* s) {
-  const int hpg = a->nheads / a->ngroups;
+// Arguments of the forward over one chunk of one batch entry (pointers are filled in by the caller).
+void chunk_args(const SsdArgs* a, int tokens, SsdArgs* s) {
   *s = *a;
   s->batch = 1;
-  s->nheads = hb;
-  s->ngroups = hb >= hpg ? hb / hpg : 1;
-  s->flags = a->flags;
+  s->seqlen = tokens;
+  s->nsegments = 0;
+  s->status = nullptr;
+  s->D = nullptr;
+  s->Z = nullptr;
 }
 
 Plan make_plan(const SsdArgs* a) {
   Plan pl{};
-  const int hpg = a->nheads / a->ngroups;
   const int e = esize(a->dtype);
-  // Largest head block (dividing the heads, compatible with the groups) whose
-  // X slice stays at or below ~32 MiB, so that several slices are in flight.
-  const size_t per_head = (size_t)a->seqlen * a->headdim * e;
-  const size_t total = per_head * a->nheads * a->batch;
-  const size_t cap = std::max<size_t>((size_t)1 << 20, std::min<size_t>((size_t)32 << 20, total / 6));
-  int best = 0;
-  for (int hb = a->nheads; hb >= 1; --hb) {
-    if (a->nheads % hb) continue;
-    if (!(hb % hpg == 0 || hpg % hb == 0)) continue;
-    if (best == 0) best = hb;
-    if (per_head * hb <= cap || hb == 1) { best = hb; break; }
-    best = hb;
-  }
-  pl.head_block = best;
-  pl.groups_block = best >= hpg ? best / hpg : 1;
-  pl.x_bytes = align_up(per_head * best, 256);
-  pl.y_bytes = pl.x_bytes;
+  // chunk length: a multiple of the caller's chunk and of the tensor-core tile (128) when the sequence allows,
+  // sized so that the X chunk is at most 24 MiB (measured: with 8 MiB chunks simultaneous copies in both directions
+  // reach 78 GB/s, with 24 MiB 82 GB/s, and the per-chunk kernel chain costs less)
+  int unit = a->chunk / gcd_int(a->chunk, 128) * 128;
+  if (a->seqlen % unit != 0) unit = a->chunk;
+  const size_t per_token = (size_t)a->nheads * a->headdim * e;
+  const size_t total = per_token * a->seqlen * a->batch;
+  const size_t cap = std::max<size_t>((size_t)1 << 20, std::min<size_t>((size_t)24 << 20, total / 8));
+  long long tokens = (long long)(cap / per_token) / unit * unit;
+  tokens = std::max<long long>(unit, std::min<long long>(tokens, a->seqlen));
+  pl.tokens = (int)tokens;
+  pl.nchunks = (a->seqlen + pl.tokens - 1) / pl.tokens;
+  pl.x_bytes = align_up(per_token * pl.tokens, 256);
   pl.a_bytes = align_up((size_t)a->seqlen * a->nheads * 4, 256);
   pl.dt_bytes = a->dt ? align_up((size_t)a->seqlen * a->nheads * e, 256) : 0;
-  pl.st_bytes = align_up((size_t)best * a->dstate * a->headdim * 4, 256);
-  pl.ld_bytes = align_up((size_t)best * 4, 256);
   pl.bc_bytes = align_up((size_t)a->seqlen * a->ngroups * a->dstate * e, 256);
+  pl.ld_bytes = align_up((size_t)a->nheads * 4, 256);
+  pl.st_bytes = align_up((size_t)a->nheads * a->dstate * a->headdim * 4, 256);
   SsdArgs s;
-  slice_args(a, best, &s);
+  chunk_args(a, pl.tokens, &s);
   pl.ws_bytes = align_up(ssd_b200_workspace_bytes(&s), 256);
-  pl.slot_bytes = pl.x_bytes + pl.y_bytes + 2 * pl.st_bytes + pl.ld_bytes + pl.ws_bytes;
-  pl.batch_bytes = 2 * pl.bc_bytes + pl.a_bytes + pl.dt_bytes;  // B, C, A, dt of one batch entry
-  pl.total_bytes = kSlots * pl.slot_bytes + 2 * pl.batch_bytes + 256;
+  if (a->seqlen % pl.tokens != 0) {   // the shorter last chunk may be cut into segments differently
+    chunk_args(a, a->seqlen % pl.tokens, &s);
+    pl.ws_bytes = std::max(pl.ws_bytes, align_up(ssd_b200_workspace_bytes(&s), 256));
+  }
+  pl.slot_bytes = 2 * pl.x_bytes + pl.ld_bytes + pl.ws_bytes;
+  // B, C, A, dt travel once per batch entry (small copies cost a fixed ~10 us each), double-buffered
+  pl.entry_bytes = 2 * pl.bc_bytes + pl.a_bytes + pl.dt_bytes;
+  // + the carried state (ping-pong), the entering state and the leaving state of a batch entry (two each)
+  pl.total_bytes = kSlots * pl.slot_bytes + 2 * pl.entry_bytes + 6 * pl.st_bytes + 256;
   return pl;
 }
 
@@ -100,13 +107,14 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
   if (reinterpret_cast<uintptr_t>(dev_scratch) & 255) return SSD_ERR_MISALIGNED;
 
   const int e = esize(host->dtype);
-  const int b = host->batch, s = host->seqlen, h = host->nheads, p = host->headdim, n = host->dstate,
-            g = host->ngroups, hb = pl.head_block, hpg = h / g;
-  const int blocks_per_batch = h / hb;
-  const int nslices = b * blocks_per_batch;
+  const int b = host->batch, s = host->seqlen, h = host->nheads, p = host->headdim, n = host->dstate, g = host->ngroups;
+  const int nslices = b * pl.nchunks;
+  const size_t np = (size_t)n * p;
 
   cudaStream_t st_in = nullptr, st_run = nullptr, st_out = nullptr;
   std::vector<cudaEvent_t> ev_in(nslices, nullptr), ev_run(nslices, nullptr), ev_out(nslices, nullptr);
+  std::vector<float> ld_host;   // per-chunk log-decay sums, added up on the host at the end
+  if (host->final_logdecay) ld_host.assign((size_t)nslices * h, 0.f);
   int rc = SSD_OK;
   auto ck = [&](cudaError_t err) { if (err != cudaSuccess && rc == SSD_OK) rc = SSD_ERR_CUDA; };
   ck(cudaStreamCreateWithFlags(&st_in, cudaStreamNonBlocking));
@@ -119,64 +127,73 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
   }
 
   char* base = static_cast<char*>(dev_scratch);
-  char* bc_base = base + kSlots * pl.slot_bytes;
+  char* entry_base = base + kSlots * pl.slot_bytes;
+  char* st_base = entry_base + 2 * pl.entry_bytes;
+  float* carry[2] = {reinterpret_cast<float*>(st_base), reinterpret_cast<float*>(st_base + pl.st_bytes)};
+  float* enter[2] = {reinterpret_cast<float*>(st_base + 2 * pl.st_bytes), reinterpret_cast<float*>(st_base + 3 * pl.st_bytes)};
+  float* leave[2] = {reinterpret_cast<float*>(st_base + 4 * pl.st_bytes), reinterpret_cast<float*>(st_base + 5 * pl.st_bytes)};
   const char* hX = static_cast<const char*>(host->X);
   const char* hB = static_cast<const char*>(host->B);
   const char* hC = static_cast<const char*>(host->C);
   const char* hD = static_cast<const char*>(host->dt);
   char* hY = static_cast<char*>(host->Y);
+  const bool want_state = host->final_state != nullptr;
 
   for (int i = 0; i < nslices && rc == SSD_OK; ++i) {
-    const int bi = i / blocks_per_batch, blk = i % blocks_per_batch, h0 = blk * hb;
+    const int bi = i / pl.nchunks, ci = i % pl.nchunks;
+    const int t0 = ci * pl.tokens, tokens = std::min(pl.tokens, s - t0);
+    const bool first = ci == 0, last = ci == pl.nchunks - 1;
     char* slot = base + (size_t)(i % kSlots) * pl.slot_bytes;
     char* dX = slot;
     char* dY = dX + pl.x_bytes;
-    char* dI = dY + pl.y_bytes;
-    char* dF = dI + pl.st_bytes;
-    char* dL = dF + pl.st_bytes;
+    char* dL = dY + pl.x_bytes;
     char* dW = dL + pl.ld_bytes;
-    char* dB = bc_base + (size_t)(bi & 1) * pl.batch_bytes;
-    char* dC = dB + pl.bc_bytes;
-    char* dA = dC + pl.bc_bytes;
-    char* dD = dA + pl.a_bytes;
+    char* eB = entry_base + (size_t)(bi & 1) * pl.entry_bytes;   // whole batch entry: B, C, A, dt
+    char* eC = eB + pl.bc_bytes;
+    char* eA = eC + pl.bc_bytes;
+    char* eD = eA + pl.a_bytes;
+    char* dB = eB + (size_t)t0 * g * n * e;
+    char* dC = eC + (size_t)t0 * g * n * e;
+    char* dA = eA + (size_t)t0 * h * 4;
+    char* dD = eD + (size_t)t0 * h * e;
+    const size_t tok0 = (size_t)bi * s + t0;   // first token of the chunk in the [b*s] token axis
 
-    // stage 1: copies in (the slot is free once the slice that used it has left)
+    // stage 1: copies in (the slot is free once the chunk that used it has left); every block is contiguous
     if (i >= kSlots) ck(cudaStreamWaitEvent(st_in, ev_out[i - kSlots], 0));
-    if (blk == 0) {
-      // B, C, A, dt of this batch entry go to the buffer last used by entry bi-2
-      if (bi >= 2) ck(cudaStreamWaitEvent(st_in, ev_run[(bi - 1) * blocks_per_batch - 1], 0));
-      const size_t bytes = (size_t)s * g * n * e;
-      ck(cudaMemcpyAsync(dB, hB + (size_t)bi * bytes, bytes, cudaMemcpyHostToDevice, st_in));
-      if (hC) ck(cudaMemcpyAsync(dC, hC + (size_t)bi * bytes, bytes, cudaMemcpyHostToDevice, st_in));
-      ck(cudaMemcpyAsync(dA, host->A + (size_t)bi * s * h, (size_t)s * h * 4, cudaMemcpyHostToDevice, st_in));
-      if (hD) ck(cudaMemcpyAsync(dD, hD + (size_t)bi * s * h * e, (size_t)s * h * e, cudaMemcpyHostToDevice, st_in));
+    if (first) {
+      // B, C, A, dt (and the entering state) of the whole batch entry; their buffers were last read by the kernels
+      // of batch entry bi-2
+      if (bi >= 2) ck(cudaStreamWaitEvent(st_in, ev_run[(bi - 1) * pl.nchunks - 1], 0));
+      const size_t row0 = (size_t)bi * s;
+      ck(cudaMemcpyAsync(eB, hB + row0 * g * n * e, (size_t)s * g * n * e, cudaMemcpyHostToDevice, st_in));
+      if (hC) ck(cudaMemcpyAsync(eC, hC + row0 * g * n * e, (size_t)s * g * n * e, cudaMemcpyHostToDevice, st_in));
+      ck(cudaMemcpyAsync(eA, host->A + row0 * h, (size_t)s * h * 4, cudaMemcpyHostToDevice, st_in));
+      if (hD) ck(cudaMemcpyAsync(eD, hD + row0 * h * e, (size_t)s * h * e, cudaMemcpyHostToDevice, st_in));
+      if (host->initial_state)
+        ck(cudaMemcpyAsync(enter[bi & 1], host->initial_state + (size_t)bi * h * np, (size_t)h * np * 4,
+                           cudaMemcpyHostToDevice, st_in));
     }
-    ck(cudaMemcpy2DAsync(dX, (size_t)hb * p * e, hX + ((size_t)bi * s * h + h0) * p * e, (size_t)h * p * e,
-                         (size_t)hb * p * e, s, cudaMemcpyHostToDevice, st_in));
-    if (host->initial_state)
-      ck(cudaMemcpyAsync(dI, host->initial_state + ((size_t)bi * h + h0) * n * p, (size_t)hb * n * p * 4,
-                         cudaMemcpyHostToDevice, st_in));
+    ck(cudaMemcpyAsync(dX, hX + tok0 * h * p * e, (size_t)tokens * h * p * e, cudaMemcpyHostToDevice, st_in));
     ck(cudaEventRecord(ev_in[i], st_in));
 
-    // stage 2: kernels
+    // stage 2: kernels; the state enters from the previous chunk of the sequence and leaves for the next one
     ck(cudaStreamWaitEvent(st_run, ev_in[i], 0));
+    if (last && want_state && bi >= 2) ck(cudaStreamWaitEvent(st_run, ev_out[(bi - 1) * pl.nchunks - 1], 0));
     SsdArgs sa;
-    slice_args(host, hb, &sa);
-    const int g0 = h0 / hpg;
-    sa.X = dX; sa.A = reinterpret_cast<const float*>(dA) + h0;
-    sa.B = dB + (size_t)g0 * n * e;
-    sa.C = hC ? dC + (size_t)g0 * n * e : nullptr;
-    sa.dt = hD ? dD + (size_t)h0 * e : nullptr;
-    sa.initial_state = host->initial_state ? reinterpret_cast<const float*>(dI) : nullptr;
+    chunk_args(host, tokens, &sa);
+    sa.X = dX; sa.A = reinterpret_cast<const float*>(dA); sa.B = dB;
+    sa.C = hC ? dC : nullptr;
+    sa.dt = hD ? dD : nullptr;
     sa.Y = state_only ? nullptr : dY;
-    sa.final_state = host->final_state ? reinterpret_cast<float*>(dF) : nullptr;
+    sa.initial_state = first ? (host->initial_state ? enter[bi & 1] : nullptr) : carry[(ci - 1) & 1];
+    sa.final_state = last ? (want_state ? leave[bi & 1] : nullptr) : carry[ci & 1];
     sa.final_logdecay = host->final_logdecay ? reinterpret_cast<float*>(dL) : nullptr;
     sa.workspace = pl.ws_bytes ? dW : nullptr;
     sa.workspace_bytes = pl.ws_bytes;
-    sa.status = nullptr;
-    const int64_t xs[3] = {(int64_t)s * hb * p, (int64_t)hb * p, p};
-    const int64_t as[3] = {(int64_t)s * h, h, 1};
-    const int64_t bs[3] = {(int64_t)s * g * n, (int64_t)g * n, n};
+    if (state_only && !sa.final_state) sa.final_state = carry[ci & 1];
+    const int64_t xs[3] = {(int64_t)tokens * h * p, (int64_t)h * p, p};
+    const int64_t as[3] = {(int64_t)tokens * h, h, 1};
+    const int64_t bs[3] = {(int64_t)tokens * g * n, (int64_t)g * n, n};
     for (int k = 0; k < 3; ++k) {
       sa.x_stride[k] = xs[k]; sa.y_stride[k] = xs[k]; sa.a_stride[k] = as[k]; sa.dt_stride[k] = as[k];
       sa.b_stride[k] = bs[k]; sa.c_stride[k] = bs[k];
@@ -190,20 +207,26 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
     // stage 3: copies out
     ck(cudaStreamWaitEvent(st_out, ev_run[i], 0));
     if (!state_only)
-      ck(cudaMemcpy2DAsync(hY + ((size_t)bi * s * h + h0) * p * e, (size_t)h * p * e, dY, (size_t)hb * p * e,
-                           (size_t)hb * p * e, s, cudaMemcpyDeviceToHost, st_out));
-    if (host->final_state)
-      ck(cudaMemcpyAsync(host->final_state + ((size_t)bi * h + h0) * n * p, dF, (size_t)hb * n * p * 4,
+      ck(cudaMemcpyAsync(hY + tok0 * h * p * e, dY, (size_t)tokens * h * p * e, cudaMemcpyDeviceToHost, st_out));
+    if (last && want_state)
+      ck(cudaMemcpyAsync(host->final_state + (size_t)bi * h * np, leave[bi & 1], (size_t)h * np * 4,
                          cudaMemcpyDeviceToHost, st_out));
     if (host->final_logdecay)
-      ck(cudaMemcpyAsync(host->final_logdecay + (size_t)bi * h + h0, dL, (size_t)hb * 4, cudaMemcpyDeviceToHost,
-                         st_out));
+      ck(cudaMemcpyAsync(ld_host.data() + (size_t)i * h, dL, (size_t)h * 4, cudaMemcpyDeviceToHost, st_out));
     ck(cudaEventRecord(ev_out[i], st_out));
   }
 
   if (st_in) ck(cudaStreamSynchronize(st_in));
   if (st_run) ck(cudaStreamSynchronize(st_run));
   if (st_out) ck(cudaStreamSynchronize(st_out));
+  if (host->final_logdecay && rc == SSD_OK) {
+    for (int bi = 0; bi < b; ++bi)
+      for (int hh = 0; hh < h; ++hh) {
+        double acc = 0.0;
+        for (int ci = 0; ci < pl.nchunks; ++ci) acc += ld_host[((size_t)bi * pl.nchunks + ci) * h + hh];
+        host->final_logdecay[(size_t)bi * h + hh] = (float)acc;
+      }
+  }
   for (auto* v : {&ev_in, &ev_run, &ev_out})
     for (cudaEvent_t ev : *v)
       if (ev) cudaEventDestroy(ev);
