@@ -424,6 +424,56 @@ def test_dt_prologue(dtype):
     assert torch.allclose(A_dt.cpu(), -torch.exp(A_log) * dt.cpu().float(), rtol=1e-6, atol=0)
 
 
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_randomised_shapes_modes_and_epilogues(seed):
+    """Seeded random draws over group layout, state size, dtype, tiles per sequence, chunk, dt, initial state,
+    segment count, state-only mode and the skip/gate epilogue (a few with enough sequences for the chained mode),
+    against the fp64 recurrence; the device status word must stay clean."""
+    import random
+
+    if not _tc_available():
+        pytest.skip("tensor-core kernel not available")
+    W = _ssd()
+    from workloadsuite_b200 import ssd as S
+
+    rnd = random.Random(seed)
+    for it in range(12):
+        n, dtype = rnd.choice([64, 128]), rnd.choice([torch.bfloat16, torch.float16])
+        g, hpg = rnd.choice([1, 2, 4]), rnd.choice([2, 4, 6])
+        h = g * hpg
+        tiles = rnd.choice([1, 2, 3, 5, 8])
+        b = rnd.choice([1, 2, 3, 5]) if it % 4 else -(-300 // h)      # every fourth draw: >= 150 head pairs
+        s = 128 * tiles
+        chunk = rnd.choice([c for c in (32, 64, 128, 256) if s % c == 0])
+        init, use_dt, epi = rnd.random() < 0.5, rnd.random() < 0.5, rnd.random() < 0.4
+        nseg = rnd.choice([None, None, 2, 3])
+        state_only = (not epi) and rnd.random() < 0.15
+        inp = O.make_inputs(b=b, s=s, h=h, p=64, n=n, g=g, dtype=dtype, init=init, seed=100 * seed + it,
+                            decay_scale=rnd.choice([1.0, 0.1, 0.02]))
+        gen = torch.Generator().manual_seed(1000 * seed + it)
+        dt = (0.02 + torch.rand(b, s, h, generator=gen)).to(dtype) if use_dt else None
+        D = torch.randn(h, generator=gen) if epi else None
+        z = torch.randn(b, s, h, 64, generator=gen).to(dtype) if epi else None
+        d = _to_dev(inp)
+        kw = dict(dt=None if dt is None else dt.to(DEV), initial_states=d.get("initial_states"), nsegments=nseg)
+        if state_only:
+            Y, H = None, W.ssd_forward(d["X"], d["A"], d["B"], d["C"], chunk, state_only=True, **kw)
+        else:
+            Y, H = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], chunk, return_final_state=True,
+                                 D=None if D is None else D.to(DEV), z=None if z is None else z.to(DEV), **kw)
+        torch.cuda.synchronize()
+        assert S.device_status(DEV) == 0
+        Yr, Hr = O.ssd_recurrence(inp["X"], inp["A"], inp["B"], inp["C"], dt=dt,
+                                  initial_states=inp.get("initial_states"), return_final_state=True)
+        herr = ((H.cpu().double() - Hr).abs().amax(dim=(2, 3)) / Hr.abs().amax(dim=(2, 3)).clamp_min(1e-30)).max().item()
+        case = dict(it=it, b=b, s=s, h=h, g=g, n=n, dtype=dtype, chunk=chunk, nseg=nseg, dt=use_dt, init=init, epi=epi)
+        assert herr < 2e-2, (case, herr)
+        if Y is not None:
+            if epi:
+                Yr = O.ssd_epilogue(Yr, inp["X"].double(), D.double(), z.double(), dtype=torch.float64)
+            assert max(O.error_metrics(Y.cpu(), Yr)) < 2e-2, case
+
+
 def test_host_buffer_forward_equals_device_forward():
     W = _ssd()
     inp = O.make_inputs(b=3, s=512, h=8, p=64, n=64, g=2, dtype=torch.bfloat16, init=True, seed=13, decay_scale=0.1)
