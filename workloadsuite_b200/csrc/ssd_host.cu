@@ -108,7 +108,46 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
 
   const int e = esize(host->dtype);
   const int b = host->batch, s = host->seqlen, h = host->nheads, p = host->headdim, n = host->dstate, g = host->ngroups;
-  const int nslices = b * pl.nchunks;
+  // The chunks of all batch entries in order.  The first entry opens and the last one closes with a ramp of smaller
+  // chunks (1/8, 1/8, 1/4, 1/2 of the regular length), so that the device->host stream starts early and the
+  // host->device stream ends late: the two directions then overlap for all but a fraction of a chunk.
+  struct Slice { int bi, ci, t0, tokens; bool first, last; };
+  std::vector<Slice> slices;
+  {
+    int unit = host->chunk / gcd_int(host->chunk, 128) * 128;
+    if (s % unit != 0) unit = host->chunk;
+    for (int bi = 0; bi < b; ++bi) {
+      std::vector<int> lens;
+      int left = s;
+      const int ramp[4] = {pl.tokens / 8, pl.tokens / 8, pl.tokens / 4, pl.tokens / 2};
+      std::vector<int> head, tail;
+      if (bi == 0)
+        for (int k = 0; k < 4; ++k) {
+          const int len = ramp[k] / unit * unit;
+          if (len > 0 && left - len >= pl.tokens) { head.push_back(len); left -= len; }
+        }
+      if (bi == b - 1)
+        for (int k = 0; k < 4; ++k) {
+          const int len = ramp[k] / unit * unit;
+          if (len > 0 && left - len >= pl.tokens) { tail.insert(tail.begin(), len); left -= len; }
+        }
+      lens = head;
+      while (left > 0) { const int len = std::min(pl.tokens, left); lens.push_back(len); left -= len; }
+      // (ramp-down pieces are listed largest first, so that the last copies are the small ones)
+      std::sort(tail.begin(), tail.end(), [](int a, int c) { return a > c; });
+      lens.insert(lens.end(), tail.begin(), tail.end());
+      int t0 = 0;
+      for (size_t k = 0; k < lens.size(); ++k) {
+        slices.push_back({bi, (int)k, t0, lens[k], k == 0, k + 1 == lens.size()});
+        t0 += lens[k];
+      }
+    }
+  }
+  const int nslices = (int)slices.size();
+  std::vector<int> entry_first(b + 1, 0);   // index of the first slice of every batch entry
+  for (int i = 0; i < nslices; ++i)
+    if (slices[i].first) entry_first[slices[i].bi] = i;
+  entry_first[b] = nslices;
   const size_t np = (size_t)n * p;
 
   cudaStream_t st_in = nullptr, st_run = nullptr, st_out = nullptr;
@@ -140,9 +179,8 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
   const bool want_state = host->final_state != nullptr;
 
   for (int i = 0; i < nslices && rc == SSD_OK; ++i) {
-    const int bi = i / pl.nchunks, ci = i % pl.nchunks;
-    const int t0 = ci * pl.tokens, tokens = std::min(pl.tokens, s - t0);
-    const bool first = ci == 0, last = ci == pl.nchunks - 1;
+    const int bi = slices[i].bi, ci = slices[i].ci, t0 = slices[i].t0, tokens = slices[i].tokens;
+    const bool first = slices[i].first, last = slices[i].last;
     char* slot = base + (size_t)(i % kSlots) * pl.slot_bytes;
     char* dX = slot;
     char* dY = dX + pl.x_bytes;
@@ -163,7 +201,7 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
     if (first) {
       // B, C, A, dt (and the entering state) of the whole batch entry; their buffers were last read by the kernels
       // of batch entry bi-2
-      if (bi >= 2) ck(cudaStreamWaitEvent(st_in, ev_run[(bi - 1) * pl.nchunks - 1], 0));
+      if (bi >= 2) ck(cudaStreamWaitEvent(st_in, ev_run[entry_first[bi - 1] - 1], 0));
       const size_t row0 = (size_t)bi * s;
       ck(cudaMemcpyAsync(eB, hB + row0 * g * n * e, (size_t)s * g * n * e, cudaMemcpyHostToDevice, st_in));
       if (hC) ck(cudaMemcpyAsync(eC, hC + row0 * g * n * e, (size_t)s * g * n * e, cudaMemcpyHostToDevice, st_in));
@@ -178,7 +216,7 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
 
     // stage 2: kernels; the state enters from the previous chunk of the sequence and leaves for the next one
     ck(cudaStreamWaitEvent(st_run, ev_in[i], 0));
-    if (last && want_state && bi >= 2) ck(cudaStreamWaitEvent(st_run, ev_out[(bi - 1) * pl.nchunks - 1], 0));
+    if (last && want_state && bi >= 2) ck(cudaStreamWaitEvent(st_run, ev_out[entry_first[bi - 1] - 1], 0));
     SsdArgs sa;
     chunk_args(host, tokens, &sa);
     sa.X = dX; sa.A = reinterpret_cast<const float*>(dA); sa.B = dB;
@@ -223,7 +261,7 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
     for (int bi = 0; bi < b; ++bi)
       for (int hh = 0; hh < h; ++hh) {
         double acc = 0.0;
-        for (int ci = 0; ci < pl.nchunks; ++ci) acc += ld_host[((size_t)bi * pl.nchunks + ci) * h + hh];
+        for (int i = entry_first[bi]; i < entry_first[bi + 1]; ++i) acc += ld_host[(size_t)i * h + hh];
         host->final_logdecay[(size_t)bi * h + hh] = (float)acc;
       }
   }
