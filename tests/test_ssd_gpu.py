@@ -502,6 +502,24 @@ def test_host_buffer_forward_carries_the_state_across_sequence_chunks():
     assert ((fin.double() - Hr).abs().max() / Hr.abs().max()).item() < 2e-2
 
 
+def test_host_buffer_forward_groups_short_batch_entries():
+    """Many short sequences: several whole batch entries travel and run as one chunk (the last group is smaller);
+    per-entry initial and final states come through."""
+    W = _ssd()
+    inp = O.make_inputs(b=37, s=256, h=8, p=64, n=64, g=2, dtype=torch.bfloat16, init=True, seed=15, decay_scale=0.05)
+    r = W.HostRunner(37, 256, 8, 64, 64, 2, 128, torch.bfloat16, device=str(DEV))
+    out = torch.empty_like(inp["X"]).pin_memory()
+    fin = torch.empty(37, 8, 64, 64).pin_memory()
+    r.run(inp["X"].pin_memory(), inp["A"].pin_memory(), inp["B"].pin_memory(), inp["C"].pin_memory(), out,
+          initial_states=inp["initial_states"].pin_memory(), final_state=fin)
+    Yr, Hr = O.ssd_recurrence(inp["X"], inp["A"], inp["B"], inp["C"], initial_states=inp["initial_states"],
+                              return_final_state=True)
+    per_bh, fro = O.error_metrics(out, Yr)
+    assert per_bh < 2e-2 and fro < 2e-2, (per_bh, fro)
+    herr = ((fin.double() - Hr).abs().amax(dim=(2, 3)) / Hr.abs().amax(dim=(2, 3)).clamp_min(1e-30)).max().item()
+    assert herr < 2e-2, herr
+
+
 def test_dropin_model_matches_reference_golden(golden_dir):
     from workloadsuite_b200 import mamba_model as M
 

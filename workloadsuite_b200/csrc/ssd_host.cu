@@ -23,6 +23,7 @@ int gcd_int(int a, int b) { return b == 0 ? a : gcd_int(b, a % b); }
 struct Plan {
   int tokens;      // tokens per chunk (the last chunk of a sequence may be shorter)
   int nchunks;     // chunks per batch entry
+  int group;       // batch entries per chunk (> 1 only when a whole entry is much smaller than a chunk)
   size_t x_bytes, a_bytes, dt_bytes, bc_bytes, ws_bytes, ld_bytes, st_bytes;   // a, dt, bc: one whole batch entry
   size_t slot_bytes, entry_bytes, total_bytes;
 };
@@ -34,14 +35,21 @@ bool basic_ok(const SsdArgs* a) {
 }
 
 // Arguments of the forward over one chunk of one batch entry (pointers are filled in by the caller).
-void chunk_args(const SsdArgs* a, int tokens, SsdArgs* s) {
+void chunk_args(const SsdArgs* a, int tokens, int entries, SsdArgs* s) {
   *s = *a;
-  s->batch = 1;
+  s->batch = entries;
   s->seqlen = tokens;
   s->nsegments = 0;
   s->status = nullptr;
   s->D = nullptr;
   s->Z = nullptr;
+  // the chunk's tensors are contiguous in the device buffers (kernel choice and scratch size depend on the strides)
+  const int64_t h = a->nheads, p = a->headdim, g = a->ngroups, n = a->dstate;
+  const int64_t xs[3] = {tokens * h * p, h * p, p}, as[3] = {tokens * h, h, 1}, bs[3] = {tokens * g * n, g * n, n};
+  for (int k = 0; k < 3; ++k) {
+    s->x_stride[k] = xs[k]; s->y_stride[k] = xs[k]; s->a_stride[k] = as[k]; s->dt_stride[k] = as[k];
+    s->b_stride[k] = bs[k]; s->c_stride[k] = bs[k];
+  }
 }
 
 Plan make_plan(const SsdArgs* a) {
@@ -59,17 +67,27 @@ Plan make_plan(const SsdArgs* a) {
   tokens = std::max<long long>(unit, std::min<long long>(tokens, a->seqlen));
   pl.tokens = (int)tokens;
   pl.nchunks = (a->seqlen + pl.tokens - 1) / pl.tokens;
-  pl.x_bytes = align_up(per_token * pl.tokens, 256);
-  pl.a_bytes = align_up((size_t)a->seqlen * a->nheads * 4, 256);
-  pl.dt_bytes = a->dt ? align_up((size_t)a->seqlen * a->nheads * e, 256) : 0;
-  pl.bc_bytes = align_up((size_t)a->seqlen * a->ngroups * a->dstate * e, 256);
-  pl.ld_bytes = align_up((size_t)a->nheads * 4, 256);
-  pl.st_bytes = align_up((size_t)a->nheads * a->dstate * a->headdim * 4, 256);
+  // short sequences: several whole batch entries (contiguous in host memory) travel and run as one chunk
+  const size_t per_entry = per_token * a->seqlen;
+  pl.group = 1;
+  if (pl.nchunks == 1 && a->batch > 1 && per_entry * 2 <= cap)
+    pl.group = (int)std::min<size_t>((size_t)a->batch, cap / per_entry);
+  const size_t k = (size_t)pl.group;
+  pl.x_bytes = align_up(per_token * pl.tokens * k, 256);
+  pl.a_bytes = align_up(k * a->seqlen * a->nheads * 4, 256);
+  pl.dt_bytes = a->dt ? align_up(k * a->seqlen * a->nheads * e, 256) : 0;
+  pl.bc_bytes = align_up(k * a->seqlen * a->ngroups * a->dstate * e, 256);
+  pl.ld_bytes = align_up(k * a->nheads * 4, 256);
+  pl.st_bytes = align_up(k * a->nheads * a->dstate * a->headdim * 4, 256);
   SsdArgs s;
-  chunk_args(a, pl.tokens, &s);
+  chunk_args(a, pl.tokens, pl.group, &s);
   pl.ws_bytes = align_up(ssd_b200_workspace_bytes(&s), 256);
+  if (pl.group > 1 && a->batch % pl.group != 0) {   // the last, smaller group
+    chunk_args(a, pl.tokens, a->batch % pl.group, &s);
+    pl.ws_bytes = std::max(pl.ws_bytes, align_up(ssd_b200_workspace_bytes(&s), 256));
+  }
   if (a->seqlen % pl.tokens != 0) {   // the shorter last chunk may be cut into segments differently
-    chunk_args(a, a->seqlen % pl.tokens, &s);
+    chunk_args(a, a->seqlen % pl.tokens, 1, &s);
     pl.ws_bytes = std::max(pl.ws_bytes, align_up(ssd_b200_workspace_bytes(&s), 256));
   }
   pl.slot_bytes = 2 * pl.x_bytes + pl.ld_bytes + pl.ws_bytes;
@@ -111,12 +129,14 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
   // The chunks of all batch entries in order.  The first entry opens and the last one closes with a ramp of smaller
   // chunks (1/8, 1/8, 1/4, 1/2 of the regular length), so that the device->host stream starts early and the
   // host->device stream ends late: the two directions then overlap for all but a fraction of a chunk.
-  struct Slice { int bi, ci, t0, tokens; bool first, last; };
+  struct Slice { int bi, nb, ci, t0, tokens; bool first, last; };   // nb batch entries from bi on
   std::vector<Slice> slices;
   {
     int unit = host->chunk / gcd_int(host->chunk, 128) * 128;
     if (s % unit != 0) unit = host->chunk;
-    for (int bi = 0; bi < b; ++bi) {
+    for (int bi = 0; bi < b && pl.group > 1; bi += pl.group)
+      slices.push_back({bi, std::min(pl.group, b - bi), 0, 0, s, true, true});
+    for (int bi = 0; bi < b && pl.group == 1; ++bi) {
       std::vector<int> lens;
       int left = s;
       const int ramp[4] = {pl.tokens / 8, pl.tokens / 8, pl.tokens / 4, pl.tokens / 2};
@@ -138,22 +158,22 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
       lens.insert(lens.end(), tail.begin(), tail.end());
       int t0 = 0;
       for (size_t k = 0; k < lens.size(); ++k) {
-        slices.push_back({bi, (int)k, t0, lens[k], k == 0, k + 1 == lens.size()});
+        slices.push_back({bi, 1, (int)k, t0, lens[k], k == 0, k + 1 == lens.size()});
         t0 += lens[k];
       }
     }
   }
   const int nslices = (int)slices.size();
-  std::vector<int> entry_first(b + 1, 0);   // index of the first slice of every batch entry
-  for (int i = 0; i < nslices; ++i)
-    if (slices[i].first) entry_first[slices[i].bi] = i;
-  entry_first[b] = nslices;
+  // The per-entry buffers (B, C, A, dt, entering and leaving state) exist twice; `set` alternates per entry (group).
+  int last_run_user[2] = {-1, -1};     // last slice whose kernels read buffer set 0 / 1
+  int last_leave_user[2] = {-1, -1};   // last slice whose final-state copy read the leaving-state buffer 0 / 1
+  int nsets_used = 0;
   const size_t np = (size_t)n * p;
 
   cudaStream_t st_in = nullptr, st_run = nullptr, st_out = nullptr;
   std::vector<cudaEvent_t> ev_in(nslices, nullptr), ev_run(nslices, nullptr), ev_out(nslices, nullptr);
   std::vector<float> ld_host;   // per-chunk log-decay sums, added up on the host at the end
-  if (host->final_logdecay) ld_host.assign((size_t)nslices * h, 0.f);
+  if (host->final_logdecay) ld_host.assign((size_t)nslices * pl.group * h, 0.f);
   int rc = SSD_OK;
   auto ck = [&](cudaError_t err) { if (err != cudaSuccess && rc == SSD_OK) rc = SSD_ERR_CUDA; };
   ck(cudaStreamCreateWithFlags(&st_in, cudaStreamNonBlocking));
@@ -179,14 +199,16 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
   const bool want_state = host->final_state != nullptr;
 
   for (int i = 0; i < nslices && rc == SSD_OK; ++i) {
-    const int bi = slices[i].bi, ci = slices[i].ci, t0 = slices[i].t0, tokens = slices[i].tokens;
+    const int bi = slices[i].bi, nb = slices[i].nb, ci = slices[i].ci, t0 = slices[i].t0, tokens = slices[i].tokens;
     const bool first = slices[i].first, last = slices[i].last;
+    if (first) ++nsets_used;
+    const int set = (nsets_used - 1) & 1;
     char* slot = base + (size_t)(i % kSlots) * pl.slot_bytes;
     char* dX = slot;
     char* dY = dX + pl.x_bytes;
     char* dL = dY + pl.x_bytes;
     char* dW = dL + pl.ld_bytes;
-    char* eB = entry_base + (size_t)(bi & 1) * pl.entry_bytes;   // whole batch entry: B, C, A, dt
+    char* eB = entry_base + (size_t)set * pl.entry_bytes;   // whole batch entries: B, C, A, dt
     char* eC = eB + pl.bc_bytes;
     char* eA = eC + pl.bc_bytes;
     char* eD = eA + pl.a_bytes;
@@ -201,41 +223,36 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
     if (first) {
       // B, C, A, dt (and the entering state) of the whole batch entry; their buffers were last read by the kernels
       // of batch entry bi-2
-      if (bi >= 2) ck(cudaStreamWaitEvent(st_in, ev_run[entry_first[bi - 1] - 1], 0));
-      const size_t row0 = (size_t)bi * s;
-      ck(cudaMemcpyAsync(eB, hB + row0 * g * n * e, (size_t)s * g * n * e, cudaMemcpyHostToDevice, st_in));
-      if (hC) ck(cudaMemcpyAsync(eC, hC + row0 * g * n * e, (size_t)s * g * n * e, cudaMemcpyHostToDevice, st_in));
-      ck(cudaMemcpyAsync(eA, host->A + row0 * h, (size_t)s * h * 4, cudaMemcpyHostToDevice, st_in));
-      if (hD) ck(cudaMemcpyAsync(eD, hD + row0 * h * e, (size_t)s * h * e, cudaMemcpyHostToDevice, st_in));
+      if (last_run_user[set] >= 0) ck(cudaStreamWaitEvent(st_in, ev_run[last_run_user[set]], 0));
+      const size_t row0 = (size_t)bi * s, rows = (size_t)nb * s;
+      ck(cudaMemcpyAsync(eB, hB + row0 * g * n * e, rows * g * n * e, cudaMemcpyHostToDevice, st_in));
+      if (hC) ck(cudaMemcpyAsync(eC, hC + row0 * g * n * e, rows * g * n * e, cudaMemcpyHostToDevice, st_in));
+      ck(cudaMemcpyAsync(eA, host->A + row0 * h, rows * h * 4, cudaMemcpyHostToDevice, st_in));
+      if (hD) ck(cudaMemcpyAsync(eD, hD + row0 * h * e, rows * h * e, cudaMemcpyHostToDevice, st_in));
       if (host->initial_state)
-        ck(cudaMemcpyAsync(enter[bi & 1], host->initial_state + (size_t)bi * h * np, (size_t)h * np * 4,
+        ck(cudaMemcpyAsync(enter[set], host->initial_state + (size_t)bi * h * np, (size_t)nb * h * np * 4,
                            cudaMemcpyHostToDevice, st_in));
     }
-    ck(cudaMemcpyAsync(dX, hX + tok0 * h * p * e, (size_t)tokens * h * p * e, cudaMemcpyHostToDevice, st_in));
+    ck(cudaMemcpyAsync(dX, hX + tok0 * h * p * e, (size_t)nb * tokens * h * p * e, cudaMemcpyHostToDevice, st_in));
+    last_run_user[set] = i;
     ck(cudaEventRecord(ev_in[i], st_in));
 
     // stage 2: kernels; the state enters from the previous chunk of the sequence and leaves for the next one
     ck(cudaStreamWaitEvent(st_run, ev_in[i], 0));
-    if (last && want_state && bi >= 2) ck(cudaStreamWaitEvent(st_run, ev_out[entry_first[bi - 1] - 1], 0));
+    if (last && want_state && last_leave_user[set] >= 0)
+      ck(cudaStreamWaitEvent(st_run, ev_out[last_leave_user[set]], 0));
     SsdArgs sa;
-    chunk_args(host, tokens, &sa);
+    chunk_args(host, tokens, nb, &sa);
     sa.X = dX; sa.A = reinterpret_cast<const float*>(dA); sa.B = dB;
     sa.C = hC ? dC : nullptr;
     sa.dt = hD ? dD : nullptr;
     sa.Y = state_only ? nullptr : dY;
-    sa.initial_state = first ? (host->initial_state ? enter[bi & 1] : nullptr) : carry[(ci - 1) & 1];
-    sa.final_state = last ? (want_state ? leave[bi & 1] : nullptr) : carry[ci & 1];
+    sa.initial_state = first ? (host->initial_state ? enter[set] : nullptr) : carry[(ci - 1) & 1];
+    sa.final_state = last ? (want_state ? leave[set] : nullptr) : carry[ci & 1];
     sa.final_logdecay = host->final_logdecay ? reinterpret_cast<float*>(dL) : nullptr;
     sa.workspace = pl.ws_bytes ? dW : nullptr;
     sa.workspace_bytes = pl.ws_bytes;
     if (state_only && !sa.final_state) sa.final_state = carry[ci & 1];
-    const int64_t xs[3] = {(int64_t)tokens * h * p, (int64_t)h * p, p};
-    const int64_t as[3] = {(int64_t)tokens * h, h, 1};
-    const int64_t bs[3] = {(int64_t)tokens * g * n, (int64_t)g * n, n};
-    for (int k = 0; k < 3; ++k) {
-      sa.x_stride[k] = xs[k]; sa.y_stride[k] = xs[k]; sa.a_stride[k] = as[k]; sa.dt_stride[k] = as[k];
-      sa.b_stride[k] = bs[k]; sa.c_stride[k] = bs[k];
-    }
     if (rc == SSD_OK) {
       const int frc = ssd_b200_forward(&sa, st_run);
       if (frc != SSD_OK) rc = frc;
@@ -245,12 +262,15 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
     // stage 3: copies out
     ck(cudaStreamWaitEvent(st_out, ev_run[i], 0));
     if (!state_only)
-      ck(cudaMemcpyAsync(hY + tok0 * h * p * e, dY, (size_t)tokens * h * p * e, cudaMemcpyDeviceToHost, st_out));
-    if (last && want_state)
-      ck(cudaMemcpyAsync(host->final_state + (size_t)bi * h * np, leave[bi & 1], (size_t)h * np * 4,
+      ck(cudaMemcpyAsync(hY + tok0 * h * p * e, dY, (size_t)nb * tokens * h * p * e, cudaMemcpyDeviceToHost, st_out));
+    if (last && want_state) {
+      ck(cudaMemcpyAsync(host->final_state + (size_t)bi * h * np, leave[set], (size_t)nb * h * np * 4,
                          cudaMemcpyDeviceToHost, st_out));
+      last_leave_user[set] = i;
+    }
     if (host->final_logdecay)
-      ck(cudaMemcpyAsync(ld_host.data() + (size_t)i * h, dL, (size_t)h * 4, cudaMemcpyDeviceToHost, st_out));
+      ck(cudaMemcpyAsync(ld_host.data() + (size_t)i * pl.group * h, dL, (size_t)nb * h * 4, cudaMemcpyDeviceToHost,
+                         st_out));
     ck(cudaEventRecord(ev_out[i], st_out));
   }
 
@@ -258,12 +278,12 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
   if (st_run) ck(cudaStreamSynchronize(st_run));
   if (st_out) ck(cudaStreamSynchronize(st_out));
   if (host->final_logdecay && rc == SSD_OK) {
-    for (int bi = 0; bi < b; ++bi)
-      for (int hh = 0; hh < h; ++hh) {
-        double acc = 0.0;
-        for (int i = entry_first[bi]; i < entry_first[bi + 1]; ++i) acc += ld_host[(size_t)i * h + hh];
-        host->final_logdecay[(size_t)bi * h + hh] = (float)acc;
-      }
+    std::vector<double> acc((size_t)b * h, 0.0);
+    for (int i = 0; i < nslices; ++i)
+      for (int eb = 0; eb < slices[i].nb; ++eb)
+        for (int hh = 0; hh < h; ++hh)
+          acc[(size_t)(slices[i].bi + eb) * h + hh] += ld_host[((size_t)i * pl.group + eb) * h + hh];
+    for (size_t k = 0; k < acc.size(); ++k) host->final_logdecay[k] = (float)acc[k];
   }
   for (auto* v : {&ev_in, &ev_run, &ev_out})
     for (cudaEvent_t ev : *v)
