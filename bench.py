@@ -11,6 +11,10 @@ sequence-parallel configuration (one all-gather of states per step).  Inputs are
 synthetic tensors with the distributions of the configuration.  Prints ONE JSON line
 on rank 0.
 
+On one GPU the line also carries ``other_configs``: the other configurations kernel-only, the default workload with
+the layer's skip/gate fused into the kernel's epilogue (next to the same steps as PyTorch passes), the conv1d+SiLU
+kernel on the workload's shape and the drop-in ``Model`` (two layers of the reference's production shape).
+
 ``--impl reference`` times the reference algorithm (the CPU restatement of
 ``SSDLayer._ssd_core`` in ``oracle/``, bit-identical to the reference in fp16) on the
 host cores, on a bounded sample of the same workload.
