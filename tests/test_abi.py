@@ -74,3 +74,52 @@ def test_python_api_has_no_cpu_path():
     B = torch.zeros(1, 64, 1, 16)
     with pytest.raises(RuntimeError, match="no CPU path"):
         ssd_forward(X, A, B, B, 64)
+
+
+def _shape(b, s, h, p, n, g, chunk, dtype):
+    a = _lib.SsdArgs()
+    a.batch, a.seqlen, a.nheads, a.headdim, a.dstate, a.ngroups, a.chunk = b, s, h, p, n, g, chunk
+    a.dtype = dtype
+    a.x_stride = (C.c_int64 * 3)(s * h * p, h * p, p)
+    a.y_stride = (C.c_int64 * 3)(s * h * p, h * p, p)
+    a.a_stride = (C.c_int64 * 3)(s * h, h, 1)
+    a.b_stride = (C.c_int64 * 3)(s * g * n, g * n, n)
+    a.c_stride = (C.c_int64 * 3)(s * g * n, g * n, n)
+    return a
+
+
+def _plan(lib, a):
+    k, nseg, launches = C.c_int32(), C.c_int32(), C.c_int32()
+    assert lib.ssd_b200_plan(C.byref(a), C.byref(k), C.byref(nseg), C.byref(launches)) == 0
+    return k.value, nseg.value, launches.value
+
+
+def test_plan_of_the_benchmark_configurations(lib):
+    """How the host logic schedules the baseline's configurations (no device involved): kernel family, cuts per
+    sequence and kernel launches."""
+    TC, SCAN = 2, 1
+    # config 2: 160 head pairs for 148 SMs -> tiles dealt out evenly inside one launch, state handed on through scratch
+    k, nseg, launches = _plan(lib, _shape(4, 8192, 80, 64, 128, 1, 256, _lib.DTYPE_BF16))
+    assert (k, launches) == (TC, 1) and nseg == 2
+    assert lib.ssd_b200_workspace_bytes(C.byref(_shape(4, 8192, 80, 64, 128, 1, 256, _lib.DTYPE_BF16))) > 0
+    # its head shards at 2 and 8 GPUs: one pass with a CTA per pair; two passes and a fold
+    assert _plan(lib, _shape(4, 8192, 40, 64, 128, 1, 256, _lib.DTYPE_BF16)) == (TC, 1, 1)
+    k, nseg, launches = _plan(lib, _shape(4, 8192, 10, 64, 128, 1, 256, _lib.DTYPE_BF16))
+    assert k == TC and nseg > 1 and launches == 3
+    # config 3 (one long sequence, 16 pairs): two passes; config 4 (6144 short sequences): whole sequences, one launch
+    k, nseg, launches = _plan(lib, _shape(1, 131072, 32, 64, 128, 1, 256, _lib.DTYPE_BF16))
+    assert k == TC and nseg > 4 and launches == 3
+    assert _plan(lib, _shape(256, 512, 48, 64, 64, 8, 128, _lib.DTYPE_BF16)) == (TC, 1, 1)
+    # config 0 is fp32: the CUDA-core recurrence
+    assert _plan(lib, _shape(16, 128, 8, 64, 16, 8, 64, _lib.DTYPE_F32))[0] == SCAN
+    # odd heads per group cannot pair up: still the tensor-core family (one head per CTA)
+    assert _plan(lib, _shape(2, 512, 3, 64, 128, 3, 128, _lib.DTYPE_F16))[0] == TC
+
+
+def test_host_pipeline_scratch_sizes(lib):
+    """The host-buffer entry sizes its device scratch from the shape alone: chunks of at most 24 MiB of X, four slots."""
+    big = lib.ssd_b200_host_scratch_bytes(C.byref(_shape(4, 8192, 80, 64, 128, 1, 256, _lib.DTYPE_BF16)))
+    small = lib.ssd_b200_host_scratch_bytes(C.byref(_shape(2, 512, 8, 64, 64, 2, 128, _lib.DTYPE_BF16)))
+    assert 0 < small < big < (1 << 30)
+    assert big >= 4 * 2 * (24 << 20) * 0.9            # X and Y of four 24 MiB chunks
+    assert lib.ssd_b200_host_scratch_bytes(C.byref(_shape(2, 500, 8, 64, 64, 2, 128, _lib.DTYPE_BF16))) == 0   # ragged
