@@ -7,7 +7,8 @@ Run in a container that has the reference checkout:
 It loads ``workloads/mamba/model_ref.py`` by file path (the way the reference's
 own ``bench.py:104-115`` does), calls ``SSDLayer._ssd_core``
 (``model_ref.py:123-162``) and the whole ``Model`` on small seeded inputs in the
-reference's native fp16 on the CPU, and stores inputs and outputs as ``.npz``.
+reference's native fp16 on the CPU, and stores inputs and outputs as ``.npz``;
+``layer_tiny`` also holds the intermediates of one ``SSDLayer.forward``.
 The fixtures pin the CPU oracle (``oracle/ssd_oracle.py``) and, through it, the
 CUDA kernels; nothing at test time needs the reference checkout.
 """
@@ -83,6 +84,48 @@ def model_case(mod, name, *, d_model, n_layers, n_heads, d_state, d_head, n_grou
     print(name, tuple(y.shape), "max|y| =", float(y.abs().max()))
 
 
+def layer_case(mod, name, *, d_model, n_heads, d_state, d_head, n_groups, block_len, b, s, seed):
+    """Intermediates of ONE unmodified ``SSDLayer.forward`` (``model_ref.py:68-121``), captured with hooks and by
+    wrapping the bound ``_ssd_core`` of the instance (the source is not touched): the projection output, what the
+    core receives (x after conv+SiLU, dt after softplus, A_dt) and returns, and what ``out_proj`` receives (the
+    core output after skip and gate)."""
+    torch.manual_seed(seed)
+    layer = mod.SSDLayer(d_model=d_model, n_heads=n_heads, d_state=d_state, d_head=d_head, n_groups=n_groups,
+                         block_len=block_len).eval()
+    with torch.no_grad():
+        layer.D.copy_(torch.randn(n_heads).half())
+        layer.dt_bias.copy_((torch.randn(n_heads) - 3.0).half())
+    cap = {}
+    layer.in_proj.register_forward_hook(lambda m, i, o: cap.__setitem__("zxbcdt", o.detach().clone()))
+    layer.out_proj.register_forward_pre_hook(lambda m, i: cap.__setitem__("y_gated", i[0].detach().clone()))
+    inner = layer._ssd_core
+
+    def spy(X_b, B_b, C_b, dt_b, A_dt_b, batch):
+        Y = inner(X_b, B_b, C_b, dt_b, A_dt_b, batch)
+        cap.update(x=X_b.detach().clone(), dt=dt_b.detach().clone(), A_dt=A_dt_b.detach().clone(),
+                   y_core=Y.detach().clone())
+        return Y
+
+    layer._ssd_core = spy
+    gen = torch.Generator().manual_seed(seed + 1)
+    u = torch.randn(b, s, d_model, generator=gen).half()
+    with torch.inference_mode():
+        out = layer(u)
+    assert torch.isfinite(out).all()
+    h, p = n_heads, d_head
+    res = {
+        "__shape": np.array([d_model, n_heads, d_state, d_head, n_groups, block_len, b, s], dtype=np.int64),
+        "u": u.numpy(), "out": out.numpy(), "zxbcdt": cap["zxbcdt"].numpy(),
+        "x": cap["x"].reshape(b, s, h, p).numpy(), "dt": cap["dt"].reshape(b, s, h).numpy(),
+        "A_dt": cap["A_dt"].reshape(b, s, h).numpy(), "y_core": cap["y_core"].reshape(b, s, h, p).numpy(),
+        "y_gated": cap["y_gated"].reshape(b, s, h, p).numpy(),
+    }
+    for k, v in layer.state_dict().items():
+        res["w." + k] = v.numpy()
+    np.savez_compressed(HERE / f"{name}.npz", **res)
+    print(name, "max|y_gated| =", float(cap["y_gated"].abs().max()))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", type=Path, required=True)
@@ -95,6 +138,8 @@ def main():
     core_case(mod, "core_n128_q128_dt", b=1, s=256, h=2, p=64, n=128, g=1, chunk=128, seed=14, with_dt=True)
     model_case(mod, "model_tiny", d_model=64, n_layers=2, n_heads=2, d_state=128, d_head=64, n_groups=1,
                block_len=64, b=2, s=128, seed=21)
+    layer_case(mod, "layer_tiny", d_model=64, n_heads=4, d_state=64, d_head=64, n_groups=2, block_len=64, b=2, s=256,
+               seed=31)
 
 
 if __name__ == "__main__":

@@ -114,3 +114,30 @@ def test_layer_oracle_reproduces_reference_model_output(golden_dir):
     assert out.dtype == ref.dtype
     err = (out.double() - ref.double()).abs().max().item() / ref.double().abs().max().item()
     assert err < 2e-3, err   # same operations in the same precision; only kernel-level summation order may differ
+
+
+def _layer_fixture(golden_dir):
+    z = np.load(golden_dir / "layer_tiny.npz")
+    d_model, h, n, p, g, block_len, b, s = [int(v) for v in z["__shape"]]
+    t = {k: torch.from_numpy(z[k]) for k in z.files if k != "__shape"}
+    d_inner, gn = h * p, g * n
+    x_raw, zz, B, C, dt_raw = torch.split(t["zxbcdt"], [d_inner, d_inner, gn, gn, h], dim=-1)
+    t.update(x_raw=x_raw, z=zz.reshape(b, s, h, p), B=B.reshape(b, s, g, n), C=C.reshape(b, s, g, n), dt_raw=dt_raw)
+    return t, block_len
+
+
+def test_oracle_pieces_equal_the_reference_layer_intermediates(golden_dir):
+    """Conv+SiLU, dt discretisation, core and skip/gate of the oracle against what the unmodified reference layer
+    computed at the same points (fixture ``layer_tiny.npz``, captured with hooks): bit-identical in fp16."""
+    import torch.nn.functional as F
+
+    t, block_len = _layer_fixture(golden_dir)
+    x = O.causal_conv1d_silu(t["x_raw"], t["w.conv1d.weight"], t["w.conv1d.bias"])
+    assert torch.equal(x.reshape(t["x"].shape), t["x"])                                    # model_ref.py:83-89
+    dt = F.softplus(t["dt_raw"] + t["w.dt_bias"])                                            # :94
+    assert torch.equal(dt, t["dt"])
+    A_dt = -torch.exp(t["w.A_log"]) * dt.float()                                             # :102-103
+    assert torch.equal(A_dt, t["A_dt"])
+    Y = O.ssd_chunked(t["x"], t["A_dt"], t["B"], t["C"], block_len, dt=t["dt"])               # :123-162
+    assert torch.equal(Y, t["y_core"])
+    assert torch.equal(O.ssd_epilogue(Y, t["x"], t["w.D"], t["z"]), t["y_gated"])             # :116-118

@@ -520,6 +520,35 @@ def test_host_buffer_forward_groups_short_batch_entries():
     assert herr < 2e-2, herr
 
 
+def test_layer_kernels_match_reference_layer_intermediates(golden_dir):
+    """Conv+SiLU, dt discretisation and core + fused skip/gate on the GPU against what the unmodified reference layer
+    computed at the same points (``layer_tiny.npz``: captured with hooks inside ``SSDLayer.forward``)."""
+    W = _ssd()
+    z = np.load(golden_dir / "layer_tiny.npz")
+    d_model, h, n, p, g, block_len, b, s = [int(v) for v in z["__shape"]]
+    t = {k: torch.from_numpy(z[k]).to(DEV) for k in z.files if k != "__shape"}
+    d_inner, gn = h * p, g * n
+    proj = t["zxbcdt"]
+    x = W.conv1d_silu(proj[..., :d_inner], t["w.conv1d.weight"], t["w.conv1d.bias"])             # model_ref.py:83-86
+    ref_x = t["x"].reshape(b, s, d_inner).double()
+    assert ((x.double() - ref_x).abs().max() / ref_x.abs().max()).item() < 5e-3
+    dt, A_dt = W.dt_prologue(proj[..., 2 * d_inner + 2 * gn:], t["w.dt_bias"], t["w.A_log"])      # :94, 102-103
+    assert ((dt.float() - t["dt"].float()).abs() / t["dt"].float().abs().clamp_min(1e-6)).max().item() < 2e-3
+    assert ((A_dt - t["A_dt"]).abs() / t["A_dt"].abs().clamp_min(1e-6)).max().item() < 2e-3
+    # core with the reference's own inputs, skip and gate fused (:123-162, 116-118)
+    B = proj[..., 2 * d_inner:2 * d_inner + gn].reshape(b, s, g, n).contiguous()
+    C_ = proj[..., 2 * d_inner + gn:2 * d_inner + 2 * gn].reshape(b, s, g, n).contiguous()
+    zz = proj[..., d_inner:2 * d_inner].reshape(b, s, h, p).contiguous()
+    for sep in (False, True):
+        Y = W.ssd_forward(t["x"], t["A_dt"], B, C_, block_len, dt=t["dt"], D=t["w.D"].float(), z=zz,
+                          separate_epilogue=sep)
+        per_bh, fro = O.error_metrics(Y.cpu(), t["y_gated"].cpu())
+        assert per_bh < 2e-2 and fro < 2e-2, (sep, per_bh, fro)
+    Yc = W.ssd_forward(t["x"], t["A_dt"], B, C_, block_len, dt=t["dt"])
+    per_bh, fro = O.error_metrics(Yc.cpu(), t["y_core"].cpu())
+    assert per_bh < 2e-2 and fro < 2e-2, (per_bh, fro)
+
+
 def test_dropin_model_matches_reference_golden(golden_dir):
     from workloadsuite_b200 import mamba_model as M
 
