@@ -320,18 +320,16 @@ int launch_scan_f32(const ScanParams& prm, int dtype, cudaStream_t stream) {
 // ---------------------------------------------------------------------------------------------
 // Skip and gate of SSDLayer.forward after the core (model_ref.py:116-118), for the kernels that do
 // not fuse it:  Y <- (Y + x * D[head]) * silu(z), fp32 arithmetic, one rounding.  One thread per
-// 8 consecutive head-dim elements (16 bytes of a 16-bit row; rows are 16-byte aligned when vec_ok).
+// 8 consecutive head-dim elements (16 bytes of a 16-bit row; rows are 16-byte aligned when vec_ok),
+// one block per token.
 template <typename T>
 __global__ void __launch_bounds__(256)
 ssd_epilogue_kernel(const ScanParams p) {
+  // one block per token row (b, t); its threads walk the row's (head, 8-element vector) pairs: 32-bit index math only
   const int vec = p.p / 8;
-  const int64_t total = (int64_t)p.batch * p.seqlen * p.nheads * vec;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int v = (int)(i % vec);
-    int64_t r = i / vec;
-    const int hh = (int)(r % p.nheads); r /= p.nheads;
-    const int t = (int)(r % p.seqlen);
-    const int b = (int)(r / p.seqlen);
+  const int b = blockIdx.x / p.seqlen, t = blockIdx.x - b * p.seqlen;
+  for (int i = threadIdx.x; i < p.nheads * vec; i += blockDim.x) {
+    const int hh = i / vec, v = i - hh * vec;
     T* y = static_cast<T*>(p.Y) + b * p.ys[0] + (int64_t)t * p.ys[1] + hh * p.ys[2] + 8 * v;
     const T* x = static_cast<const T*>(p.X) + b * p.xs[0] + (int64_t)t * p.xs[1] + hh * p.xs[2] + 8 * v;
     const T* z = p.Z ? static_cast<const T*>(p.Z) + b * p.zs[0] + (int64_t)t * p.zs[1] + hh * p.zs[2] + 8 * v : nullptr;
@@ -377,11 +375,14 @@ ssd_epilogue_kernel(const ScanParams p) {
 int launch_epilogue(const ScanParams& p, int dtype, cudaStream_t stream) {
   if (!p.D && !p.Z) return SSD_OK;
   if (p.p % 8 != 0) return SSD_ERR_UNSUPPORTED;
-  const int64_t total = (int64_t)p.batch * p.seqlen * p.nheads * (p.p / 8);
-  const int grid = (int)std::min<int64_t>((total + 255) / 256, 148 * 16);
-  if (dtype == SSD_DTYPE_F32) ssd_epilogue_kernel<float><<<grid, 256, 0, stream>>>(p);
-  else if (dtype == SSD_DTYPE_F16) ssd_epilogue_kernel<__half><<<grid, 256, 0, stream>>>(p);
-  else ssd_epilogue_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);
+  const int64_t rows = (int64_t)p.batch * p.seqlen;
+  if (rows > 0x7fffffffLL) return SSD_ERR_TOO_LARGE;
+  const int grid = (int)rows;
+  const int work = p.nheads * (p.p / 8);
+  const int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
+  if (dtype == SSD_DTYPE_F32) ssd_epilogue_kernel<float><<<grid, threads, 0, stream>>>(p);
+  else if (dtype == SSD_DTYPE_F16) ssd_epilogue_kernel<__half><<<grid, threads, 0, stream>>>(p);
+  else ssd_epilogue_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? SSD_OK : SSD_ERR_CUDA;
 }
 
