@@ -7,17 +7,30 @@ One "step" is one SSD forward over the whole workload.  Default workload: the
 Mamba-2-2.7B layer shape (batch 4, seq 8192, 80 heads, d_head 64, d_state 128, chunk
 256, one B/C group, bf16 with fp32 log-decay), head-sharded over N GPUs with no
 collective (total work fixed: strong scaling).  ``--workload cfg3`` runs the 128K-token
-sequence-parallel configuration (one all-gather of states per step).  Inputs are seeded
-synthetic tensors with the distributions of the configuration.  Prints ONE JSON line
-on rank 0.
+sequence-parallel configuration (one exchange of states per step); with more than one
+GPU it is also timed after the default workload and reported under
+``other_configs["cfg3:seqN"]``.  Inputs are seeded synthetic tensors with the
+distributions of the configuration.  Prints ONE JSON line on rank 0.
 
-On one GPU the line also carries ``other_configs``: the other configurations kernel-only, the default workload with
-the layer's skip/gate fused into the kernel's epilogue (next to the same steps as PyTorch passes), the conv1d+SiLU
-kernel on the workload's shape and the drop-in ``Model`` (two layers of the reference's production shape).
+Before anything is timed, at every N, a small slow-decay case (cross-chunk and cross-shard
+terms matter) is cut the way the timed workload is sharded, run through the same code path,
+gathered on rank 0 and compared with the float64 recurrence of ``oracle/``; the result is the
+``parity`` object of the line and a failure ends the run with a non-zero exit code.
 
-``--impl reference`` times the reference algorithm (the CPU restatement of
-``SSDLayer._ssd_core`` in ``oracle/``, bit-identical to the reference in fp16) on the
-host cores, on a bounded sample of the same workload.
+The ``--steps`` block is repeated until at least half a second of GPU time has been measured;
+``ms_per_step`` is the median block (each block: barrier + synchronize on both sides, CUDA
+events, max over ranks).
+
+On one GPU the line also carries ``other_configs``: the other configurations kernel-only, the
+default workload with the layer's skip/gate fused into the kernel's epilogue (next to the same
+steps as PyTorch passes), the conv1d+SiLU kernel on the workload's shape, and the drop-in
+``Model`` next to the reference ``Model`` timed by the reference's own harness functions.
+
+``--impl reference`` times the reference's own ``SSDLayer._ssd_core`` (``model_ref.py:123-162``:
+the bytecode that ``oracle/build_ref.py`` compiles from the unmodified reference into
+``oracle/_ref/``; the oracle's bit-identical restatement when that directory was never built, and
+for the fp32 configuration, which the fp16-only reference cannot run) on all host cores, on a
+bounded sample of the same workload.
 """
 from __future__ import annotations
 
@@ -25,6 +38,7 @@ import argparse
 import json
 import math
 import os
+import re
 import statistics
 import sys
 import threading
@@ -52,11 +66,15 @@ WORKLOAD_NAMES = {
 }
 TDT = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
 L2_BYTES = 126e6
+MIN_TIMED_SECONDS = 0.5
+PARITY_TOL = {"f32": 1e-4, "bf16": 2e-2, "f16": 2e-2}
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu capture summarised
-# in profiles/ssd_tc2_kernel_cfg2.md (same command line as this bench, --steps 2 --warmup 3); None where no capture
-# of that (workload, kernel, world size) exists.
-NCU_TRAFFIC_BYTES = {("cfg2", "tcgen05", 1): 666.1e6}
+
+def line_config(name, world, seq_parallel):
+    """The ``config`` object: the same keys and values in both arms (``--impl reference`` included)."""
+    return {"workload": WORKLOAD_NAMES[name], "name": name,
+            "parallelism": ("seq%d+state-exchange" % world) if seq_parallel else ("heads%d" % world),
+            "l2": "rotating input sets larger than L2 between timed iterations"}
 
 
 def algorithmic_bytes(cfg, h=None, s=None):
@@ -174,16 +192,56 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
+def captured_traffic(workload, world):
+    """DRAM bytes (read + write) of one launch of the dominant kernel from the ncu summary under ``profiles/``,
+    or None.  A summary counts only if it names this workload at one GPU and was captured from the kernels
+    that run now: its ``kernel sources`` line must equal the fingerprint of the package's CUDA sources."""
+    if world != 1:
+        return None
+    try:
+        from workloadsuite_b200 import build as B
+
+        stamp = B.source_fingerprint()
+        for f in sorted((ROOT / "profiles").glob("*.md")):
+            m = re.search(r"^traffic_bytes_per_launch:\s*([0-9.eE+]+)\s+workload:\s*(\w+)\s+kernel sources:\s*(\w+)",
+                          f.read_text(), re.M)
+            if m and m.group(2) == workload and stamp.startswith(m.group(3)):
+                return float(m.group(1))
+    except Exception:
+        pass
+    return None
+
+
 # ----------------------------------------------------------------------------- reference (CPU) arm
 
+def reference_callable(cfg):
+    """(fn(inp, Bh, Ch) -> Y, kind): the unmodified reference core when ``oracle/_ref`` is built and the
+    configuration is half precision (the reference is hard-wired to fp16, model_ref.py:145), else the port."""
+    from oracle import build_ref as R
+    from oracle import ssd_oracle as O
+
+    mod = None
+    if cfg["dtype"] != "f32":
+        try:
+            mod = R.load_model_ref()
+        except Exception:
+            mod = None
+    if mod is not None:
+        return (lambda inp, Bh, Ch: R.reference_core(mod, inp["X"], inp["A"], Bh, Ch, cfg["chunk"])), "reference"
+    dtype = torch.float32 if cfg["dtype"] == "f32" else torch.float16
+    return (lambda inp, Bh, Ch: O.ssd_chunked(inp["X"], inp["A"], Bh, Ch, cfg["chunk"], dtype=dtype)), "port"
+
+
 def cpu_reference_sample(cfg, steps, warmup):
-    """Times the reference algorithm (oracle port, fp16 as in the reference) on host cores.
+    """Times the reference core (fp16 as in the reference) on all host cores.
 
     Sample: one batch entry of the workload with all heads and the full sequence (for the
     128K configuration a 16K-token prefix), B/C broadcast to heads outside the timed
     region as the reference's caller does (model_ref.py:97-99)."""
     from oracle import ssd_oracle as O
 
+    # a launcher such as torchrun exports OMP_NUM_THREADS=1 to its workers: use the host's cores anyway
+    torch.set_num_threads(os.cpu_count() or 1)
     b, s, h = 1, min(cfg["s"], 16384), cfg["h"]
     c = dict(cfg)
     c.update(b=b, s=s)
@@ -191,32 +249,33 @@ def cpu_reference_sample(cfg, steps, warmup):
     inp = O.make_inputs(seed=0, **{**c, "dtype": dtype})
     Bh = inp["B"].repeat_interleave(h // c["g"], dim=2).contiguous()
     Ch = inp["C"].repeat_interleave(h // c["g"], dim=2).contiguous()
+    fn, kind = reference_callable(cfg)
     times = []
     with torch.inference_mode():
         for i in range(warmup + steps):
             t0 = time.perf_counter()
-            O.ssd_chunked(inp["X"], inp["A"], Bh, Ch, c["chunk"], dtype=dtype)
+            fn(inp, Bh, Ch)
             dt = time.perf_counter() - t0
             if i >= warmup:
                 times.append(dt)
     med = statistics.median(times)
     sample = f"batch 1 of {cfg['b']}, seq {s} of {cfg['s']}, all {h} heads, {dtype}".replace("torch.", "")
-    return b * s / med, med, sample
+    return b * s / med, med, sample, kind
 
 
-def run_reference(args, cfg, rank):
+def run_reference(args, cfg, rank, world):
     if rank != 0:
         return
     steps, warmup = max(1, args.steps), max(0, args.warmup)
-    steps, warmup = min(steps, 5), min(warmup, 2)
-    tps, med, sample = cpu_reference_sample(cfg, steps, warmup)
+    tps, med, sample, kind = cpu_reference_sample(cfg, steps, warmup)
+    seq_parallel = args.workload == "cfg3" and world > 1
     line = {
         "impl": "reference", "metric": "ssd_forward_tokens_per_s", "value": tps, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": med * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f16" if cfg["dtype"] != "f32" else "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD_NAMES[args.workload], "name": args.workload},
-        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+        "config": line_config(args.workload, world, seq_parallel),
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": kind,
                          "sample": sample, "host_cpus": os.cpu_count()},
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -226,32 +285,209 @@ def run_reference(args, cfg, rank):
 
 # ----------------------------------------------------------------------------- our arm
 
-def time_steps(fn, nsets, steps, warmup, dist_on):
+def time_blocks(fn, nsets, steps, warmup, dist_on, min_seconds=MIN_TIMED_SECONDS, max_blocks=500):
+    """Warm up, then time blocks of exactly ``steps`` steps -- each bracketed by barrier + synchronize, CUDA
+    events on the current stream, max over ranks -- until ``min_seconds`` of GPU time have been measured.
+    Returns (median block ms / steps, wall t0, wall t1, list of block ms)."""
     import torch.distributed as dist
 
     for i in range(warmup):
         fn(i % nsets)
-    torch.cuda.synchronize()
-    if dist_on:
-        dist.barrier()
-    torch.cuda.synchronize()
     e0 = torch.cuda.Event(enable_timing=True)
     e1 = torch.cuda.Event(enable_timing=True)
+
+    def one_block():
+        torch.cuda.synchronize()
+        if dist_on:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(steps):
+            fn(i % nsets)
+        e1.record()
+        torch.cuda.synchronize()
+        if dist_on:
+            dist.barrier()
+        ms = e0.elapsed_time(e1)
+        if dist_on:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
     t0 = time.perf_counter()
-    e0.record()
-    for i in range(steps):
-        fn(i % nsets)
-    e1.record()
-    torch.cuda.synchronize()
+    blocks = [one_block()]
+    # (the first block's time is already the max over ranks, so every rank derives the same count)
+    nblocks = min(max_blocks, max(1, int(math.ceil(min_seconds * 1e3 / max(blocks[0], 1e-3)))))
+    for _ in range(nblocks - 1):
+        blocks.append(one_block())
     t1 = time.perf_counter()
-    if dist_on:
-        dist.barrier()
-    ms = e0.elapsed_time(e1)
-    if dist_on:
-        t = torch.tensor([ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    return ms / steps, t0, t1
+    return statistics.median(blocks) / steps, t0, t1, blocks
+
+
+def parity_leg(mode, rank, world, dev, kw):
+    """A small slow-decay case cut the way the timed workload is sharded, run through the same code path,
+    gathered on rank 0 and compared with the float64 recurrence (oracle).  Returns the ``parity`` object
+    (on every rank: the verdict is broadcast)."""
+    import torch.distributed as dist
+
+    import workloadsuite_b200 as W
+    from oracle import ssd_oracle as O
+    from workloadsuite_b200 import sharded
+
+    if mode == "seq":
+        case = dict(b=1, s=1024 * max(world, 2), h=4, p=64, n=128, g=1, dtype="bf16", decay="mamba", chunk=256)
+    else:
+        case = dict(b=2, s=1024, h=16, p=64, n=128, g=1, dtype="bf16", decay="mamba", chunk=256)
+    inp = O.make_inputs(seed=4242, decay_scale=0.02, **case)       # the same tensors on every rank
+    chunk = case["chunk"]
+    if mode == "seq" and world > 1:
+        s_loc = case["s"] // world
+        sl = slice(rank * s_loc, (rank + 1) * s_loc)
+        d = {k: v[:, sl].contiguous().to(dev) for k, v in inp.items()}
+        eng = sharded.SequenceShardedSSD()
+        Yl = eng.forward(d["X"], d["A"], d["B"], d["C"], chunk, **kw)
+        cat_dim = 1
+    else:
+        full = {k: v.to(dev) for k, v in inp.items()}
+        d = sharded.shard_heads(full["X"], full["A"], full["B"], full["C"], rank, world) if world > 1 else full
+        Yl = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], chunk, **kw)
+        cat_dim = 2
+    torch.cuda.synchronize()
+    status = W.device_status(dev)
+    if world > 1:
+        parts = [torch.empty_like(Yl) for _ in range(world)] if rank == 0 else None
+        dist.gather(Yl.contiguous(), parts, dst=0)
+        Y = torch.cat(parts, dim=cat_dim) if rank == 0 else None
+    else:
+        Y = Yl
+    verdict = torch.zeros(4, dtype=torch.float64, device=dev)
+    if rank == 0:
+        Yr = O.ssd_recurrence(inp["X"], inp["A"], inp["B"], inp["C"])
+        per_bh, fro = O.error_metrics(Y.cpu(), Yr)
+        tol = PARITY_TOL[case["dtype"]]
+        ok = per_bh < tol and fro < tol and bool(torch.isfinite(Y).all())
+        verdict = torch.tensor([per_bh, fro, tol, 1.0 if ok else 0.0], dtype=torch.float64, device=dev)
+    st = torch.tensor([float(status)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.broadcast(verdict, src=0)
+        dist.all_reduce(st, op=dist.ReduceOp.MAX)
+    per_bh, fro, tol, ok = [float(v) for v in verdict.tolist()]
+    return {"per_bh": per_bh, "fro": fro, "tol": tol, "ok": bool(ok) and st.item() == 0, "device_status": int(st.item()),
+            "against": "float64 token recurrence (oracle)",
+            "case": ("sequence-sharded " if mode == "seq" else "head-sharded ") +
+                    f"b{case['b']} s{case['s']} h{case['h']} p64 n128 bf16, log-decay x0.02, {world} rank(s)"}
+
+
+def build_step(W, sharded, cfg, rank, world, dev, kw, no_graphs, seq_parallel):
+    """Inputs, step function (CUDA-graph replay where possible) and launch accounting for one workload."""
+    if seq_parallel:
+        s_loc, h_loc = cfg["s"] // world, cfg["h"]
+    else:
+        h0, h1, _, _ = sharded.head_shard_bounds(cfg["h"], cfg["g"], rank, world)
+        s_loc, h_loc = cfg["s"], h1 - h0
+    set_bytes = algorithmic_bytes(cfg, h=h_loc, s=s_loc)
+    nsets = min(16, max(2, int(math.ceil(2.5 * L2_BYTES / set_bytes))))
+    sets = [gen_inputs(cfg, dev, seed=1000 * rank + i, h=h_loc, s=s_loc) for i in range(nsets)]
+    outs = [torch.empty_like(sets[i]["X"]) for i in range(nsets)]
+    chunk = cfg["chunk"]
+    plan = W.plan(sets[0]["X"], sets[0]["A"], sets[0]["B"], sets[0]["C"], chunk, **kw)
+    info = dict(set_bytes=set_bytes, nsets=nsets, plan=plan, s_loc=s_loc, h_loc=h_loc,
+                kernel=W.kernel_name(sets[0]["X"], sets[0]["A"], sets[0]["B"], sets[0]["C"], chunk,
+                                     kernel=kw.get("kernel")))
+    if seq_parallel:
+        eng = sharded.SequenceShardedSSD(cuda_graphs=not no_graphs)
+        info["launches"] = eng.launches_per_step(sets[0]["X"], sets[0]["A"], sets[0]["B"], sets[0]["C"], chunk, **kw)
+        info["launch_mode"] = eng.launch_mode()
+
+        def step(i):
+            d = sets[i]
+            eng.forward(d["X"], d["A"], d["B"], d["C"], chunk, out=outs[i], **kw)
+
+        info["engine"] = eng
+        return sets, outs, step, info
+
+    info["launches"] = plan["launches"]
+
+    def step(i):
+        d = sets[i]
+        W.ssd_forward(d["X"], d["A"], d["B"], d["C"], chunk, initial_states=d.get("initial_states"), out=outs[i], **kw)
+
+    # A step is a fixed sequence of launches: capture it once per input set and replay, so that the
+    # timed region measures the GPU and not the Python/driver launch path (which dominates at N=8).
+    info["launch_mode"] = "eager"
+    run_step = step
+    if not no_graphs:
+        try:
+            for i in range(nsets):
+                step(i)                      # allocates the workspace outside capture
+            torch.cuda.synchronize()
+            cap = torch.cuda.Stream()
+            graphs = []
+            with torch.cuda.stream(cap):
+                for i in range(nsets):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=cap):
+                        step(i)
+                    graphs.append(g)
+            torch.cuda.synchronize()
+
+            def run_step(i, graphs=graphs):
+                graphs[i].replay()
+
+            info["launch_mode"] = "cuda_graph"
+        except Exception as exc:  # fall back to plain launches
+            sys.stderr.write(f"[bench] CUDA graph capture failed ({type(exc).__name__}: {exc}); timing eager launches\n")
+            run_step = step
+    return sets, outs, run_step, info
+
+
+def model_through_reference_harness(dev, steps):
+    """The drop-in ``Model`` and the reference ``Model`` (``model_ref.py:165-229``, production configuration: 24
+    layers, b8 s2048 d_model 2048, fp16) timed on this GPU by the reference's own ``_benchmark``
+    (``bench.py:138-170``) under ``torch.inference_mode()`` as ``_bench_workload`` does (``bench.py:230-233``), with
+    shared weights, plus the output parity of the two on sampled rows."""
+    from oracle import build_ref as R
+    from workloadsuite_b200 import mamba_model as MM
+
+    out = {"shape": "24 layers, b8 s2048 d_model2048 h128 p64 n128 g8 block64 fp16"}
+    rb, rm = R.load_ref_bench(), R.load_model_ref()
+    init = MM.get_init_inputs()
+    torch.manual_seed(0)
+    ours = MM.Model(*init).to(dev).eval()
+    x = torch.randn(MM.batch_size, MM.seq_length, MM.d_model, dtype=torch.float16, device=dev)
+    runs = max(3, min(10, steps // 5))
+    if rb is None or rm is None:
+        out["reference"] = "oracle/_ref was not built on this machine: drop-in Model only"
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.inference_mode():
+            for _ in range(2):
+                ours(x)
+            e0.record()
+            for _ in range(runs):
+                ours(x)
+            e1.record()
+        torch.cuda.synchronize()
+        out["dropin"] = {"median_ms": e0.elapsed_time(e1) / runs}
+        return out
+    common = dict(device_type="cuda", warmup=2, runs=runs)
+    with torch.inference_mode():
+        out["dropin"] = rb._benchmark(ours, [x], **common)
+        yo = ours(x)
+    ref = rm.Model(*init).to(dev).eval()
+    ref.load_state_dict(ours.state_dict(), strict=True)
+    with torch.inference_mode():
+        out["reference_eager"] = rb._benchmark(ref, [x], **common)
+        yr = ref(x)
+    rows = torch.linspace(0, MM.seq_length - 1, 64, device=dev).long()
+    a, b_ = yo[:, rows].double(), yr[:, rows].double()
+    out["parity_sampled_rows"] = {"max_abs_err_over_max_abs_ref": float((a - b_).abs().max() / b_.abs().max()),
+                                  "tol": 2e-2, "finite": bool(torch.isfinite(yo).all())}
+    out["speedup_vs_reference_eager"] = out["reference_eager"]["median_ms"] / out["dropin"]["median_ms"]
+    out["tokens_per_s"] = MM.batch_size * MM.seq_length / (out["dropin"]["median_ms"] * 1e-3)
+    del ref, ours
+    torch.cuda.empty_cache()
+    return out
 
 
 def main():
@@ -266,6 +502,9 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-others", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the parity leg (profiling runs only)")
+    ap.add_argument("--min-seconds", type=float, default=MIN_TIMED_SECONDS,
+                    help="repeat the --steps block until this much GPU time has been measured")
     ap.add_argument("--no-graphs", action="store_true",
                     help="launch every step from Python instead of replaying one CUDA graph per input set")
     args = ap.parse_args()
@@ -277,7 +516,7 @@ def main():
     cfg = CONFIGS[args.workload]
 
     if args.impl == "reference":
-        run_reference(args, cfg, rank)
+        run_reference(args, cfg, rank, world)
         return
 
     if not torch.cuda.is_available():
@@ -293,85 +532,37 @@ def main():
     if dist_on:
         dist.init_process_group("nccl", device_id=dev)
     n_gpus = world
-
-    seq_parallel = args.workload == "cfg3" and world > 1
-    if seq_parallel:
-        s_loc, h_loc = cfg["s"] // world, cfg["h"]
-    else:
-        h0, h1, _, _ = sharded.head_shard_bounds(cfg["h"], cfg["g"], rank, world)
-        s_loc, h_loc = cfg["s"], h1 - h0
-    set_bytes = algorithmic_bytes(cfg, h=h_loc, s=s_loc)
-    nsets = max(2, int(math.ceil(2.5 * L2_BYTES / set_bytes)))
-    nsets = min(nsets, 16)
-    sets = [gen_inputs(cfg, dev, seed=1000 * rank + i, h=h_loc, s=s_loc) for i in range(nsets)]
-    outs = [torch.empty_like(sets[i]["X"]) for i in range(nsets)]
-    chunk = cfg["chunk"]
     kw = dict(kernel=args.kernel, nsegments=args.nsegments or None)
+    seq_parallel = args.workload == "cfg3" and world > 1
 
-    plan = W.plan(sets[0]["X"], sets[0]["A"], sets[0]["B"], sets[0]["C"], chunk, **kw)
-    if seq_parallel:
-        # state-only run + cross-rank fold + seeded run that reuses the per-segment states (NCCL's own
-        # all-gather kernel and two small copies into the send buffer are not counted)
-        p_state = W.plan(sets[0]["X"], sets[0]["A"], sets[0]["B"], sets[0]["C"], chunk, state_only=True, **kw)
-        seeded = plan["launches"] - 1 if plan["nsegments"] > 1 and plan["launches"] == 3 else plan["launches"]
-        launches_per_step = [p_state["launches"] + 1 + seeded]
-    else:
-        launches_per_step = [plan["launches"]]
-    if seq_parallel:
-        # the local phases replay CUDA graphs; the all-gather is launched normally
-        eng = sharded.SequenceShardedSSD(cuda_graphs=not args.no_graphs)
+    # ---- parity before timing, through the code path that is timed
+    parity = None
+    if not args.no_parity:
+        parity = parity_leg("seq" if seq_parallel else "heads", rank, world, dev, kw)
+        if not parity["ok"]:
+            if rank == 0:
+                print(json.dumps({"metric": "ssd_forward_tokens_per_s", "value": None, "n_gpus": n_gpus,
+                                  "parity": parity, "error": "parity leg failed; nothing was timed"}), flush=True)
+            if dist_on:
+                dist.destroy_process_group()
+            raise SystemExit(3)
 
-        def step(i):
-            d = sets[i]
-            eng.forward(d["X"], d["A"], d["B"], d["C"], chunk, out=outs[i], **kw)
-    else:
-        def step(i):
-            d = sets[i]
-            W.ssd_forward(d["X"], d["A"], d["B"], d["C"], chunk, initial_states=d.get("initial_states"),
-                          out=outs[i], **kw)
-
-    # A step is a fixed sequence of launches: capture it once per input set and replay, so that the
-    # timed region measures the GPU and not the Python/driver launch path (which dominates at N=8).
-    launch_mode = "eager"
-    run_step = step
-    if seq_parallel:
-        launch_mode = "eager" if args.no_graphs else "cuda_graph (local phases) + eager all-gather"
-    elif not args.no_graphs:
-        try:
-            for i in range(nsets):
-                step(i)                      # allocates the workspace and warms NCCL outside capture
-            torch.cuda.synchronize()
-            cap = torch.cuda.Stream()
-            graphs = []
-            with torch.cuda.stream(cap):
-                for i in range(nsets):
-                    g = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(g, stream=cap):
-                        step(i)
-                    graphs.append(g)
-            torch.cuda.synchronize()
-
-            def run_step(i, graphs=graphs):
-                graphs[i].replay()
-
-            launch_mode = "cuda_graph"
-        except Exception as exc:  # fall back to plain launches
-            sys.stderr.write(f"[bench] CUDA graph capture failed ({type(exc).__name__}: {exc}); timing eager launches\n")
-            run_step = step
-            launch_mode = "eager"
+    sets, outs, run_step, info = build_step(W, sharded, cfg, rank, world, dev, kw, args.no_graphs, seq_parallel)
+    set_bytes, nsets, plan = info["set_bytes"], info["nsets"], info["plan"]
 
     sampler = ClockSampler(local)
     sampler.start()
-    ms_step, t0, t1 = time_steps(run_step, nsets, args.steps, args.warmup, dist_on)
+    ms_step, t0, t1, blocks = time_blocks(run_step, nsets, args.steps, args.warmup, dist_on, args.min_seconds)
     sampler.stop()
     clocks = sampler.summary(t0, t1)
+    phases = info["engine"].phase_times_ms() if "engine" in info else None
 
     tokens = cfg["b"] * cfg["s"]
     value = tokens / (ms_step * 1e-3)
     peak, peak_kind = measured_peaks()
     total_bytes = algorithmic_bytes(cfg)          # whole job
     achieved = set_bytes / (ms_step * 1e-3) / 1e9  # this GPU's share over the step time
-    kname = W.kernel_name(sets[0]["X"], sets[0]["A"], sets[0]["B"], sets[0]["C"], chunk, kernel=args.kernel)
+    kname = info["kernel"]
 
     # ---- end to end through the host-buffer entry point (pinned host tensors, copies timed)
     e2e = None
@@ -380,8 +571,8 @@ def main():
             raise RuntimeError("skipped (--e2e-steps 0)")
         hs = {k: v.cpu().pin_memory() for k, v in sets[0].items()}
         hout = torch.empty_like(hs["X"]).pin_memory()
-        runner = W.HostRunner(cfg["b"], s_loc, h_loc, cfg["p"], cfg["n"], sets[0]["B"].shape[2], chunk,
-                              TDT[cfg["dtype"]], device=dev, kernel=args.kernel)
+        runner = W.HostRunner(cfg["b"], info["s_loc"], info["h_loc"], cfg["p"], cfg["n"], sets[0]["B"].shape[2],
+                              cfg["chunk"], TDT[cfg["dtype"]], device=dev, kernel=args.kernel)
         runner.run(hs["X"], hs["A"], hs["B"], hs["C"], hout, initial_states=hs.get("initial_states"))
         if dist_on:
             dist.barrier()
@@ -403,32 +594,45 @@ def main():
     except Exception as exc:  # report rather than lose the device-side numbers
         e2e = {"value": None, "unit": "tokens/s", "error": f"{type(exc).__name__}: {exc}"}
 
-    # ---- other configurations, kernel-only, single GPU
     others = {}
+    del sets, outs, run_step
+    info.pop("engine", None)
+    torch.cuda.empty_cache()
+
+    # ---- more than one GPU: the 128K sequence-parallel configuration too, with its own parity leg
+    if world > 1 and args.workload != "cfg3" and not args.no_others:
+        key = "cfg3:seq%d" % world
+        try:
+            c3 = CONFIGS["cfg3"]
+            p3 = None if args.no_parity else parity_leg("seq", rank, world, dev, kw)
+            s3, o3, step3, info3 = build_step(W, sharded, c3, rank, world, dev, kw, args.no_graphs, True)
+            ms3, _, _, blocks3 = time_blocks(step3, info3["nsets"], max(5, args.steps // 2), 3, dist_on, args.min_seconds)
+            others[key] = {"tokens_per_s": c3["b"] * c3["s"] / (ms3 * 1e-3), "ms_per_step": ms3, "blocks": len(blocks3),
+                           "hbm_frac_of_measured": info3["set_bytes"] / (ms3 * 1e-3) / 1e9 / peak,
+                           "launch": info3["launch_mode"], "kernel_launches_per_step": info3["launches"],
+                           "segments_per_sequence": info3["plan"]["nsegments"], "parity": p3,
+                           "phases_ms": info3["engine"].phase_times_ms()}
+            del s3, o3, step3, info3
+            torch.cuda.empty_cache()
+        except Exception as exc:
+            others[key] = {"error": f"{type(exc).__name__}: {exc}"}
+
+    # ---- other configurations, kernel-only, single GPU
     if world == 1 and not args.no_others:
-        del sets, outs
-        torch.cuda.empty_cache()
         for name in ("cfg0", "cfg1", "cfg3", "cfg4"):
             if name == args.workload:
                 continue
             try:
                 c = CONFIGS[name]
-                sb = algorithmic_bytes(c)
-                ns = min(16, max(2, int(math.ceil(2.5 * L2_BYTES / sb))))
-                ss = [gen_inputs(c, dev, seed=77 + i) for i in range(ns)]
-                oo = [torch.empty_like(x["X"]) for x in ss]
-
-                def st(i, ss=ss, oo=oo, c=c):
-                    d = ss[i]
-                    W.ssd_forward(d["X"], d["A"], d["B"], d["C"], c["chunk"],
-                                  initial_states=d.get("initial_states"), out=oo[i], kernel=args.kernel)
-
-                ms, _, _ = time_steps(st, ns, max(5, args.steps // 2), 3, False)
+                ss, oo, st, inf = build_step(W, sharded, c, 0, 1, dev, dict(kernel=args.kernel, nsegments=None),
+                                             args.no_graphs, False)
+                ms, _, _, bl = time_blocks(st, inf["nsets"], max(5, args.steps // 2), 3, False, args.min_seconds / 2)
                 others[name] = {"tokens_per_s": c["b"] * c["s"] / (ms * 1e-3), "ms_per_step": ms,
-                                "hbm_frac_of_measured": sb / (ms * 1e-3) / 1e9 / peak,
-                                "kernel": W.kernel_name(ss[0]["X"], ss[0]["A"], ss[0]["B"], ss[0]["C"], c["chunk"],
-                                                        kernel=args.kernel)}
-                del ss, oo
+                                "hbm_frac_of_measured": inf["set_bytes"] / (ms * 1e-3) / 1e9 / peak,
+                                "kernel": inf["kernel"], "launch": inf["launch_mode"],
+                                "segments_per_sequence": inf["plan"]["nsegments"],
+                                "kernel_launches_per_step": inf["launches"]}
+                del ss, oo, st
                 torch.cuda.empty_cache()
             except Exception as exc:
                 others[name] = {"error": f"{type(exc).__name__}: {exc}"}
@@ -456,8 +660,8 @@ def main():
                 Y = Y + d["X"] * Dv.to(Y.dtype).view(1, 1, -1, 1)
                 Y = Y * torch.nn.functional.silu(zz[i])
 
-            ms_f, _, _ = time_steps(st_fused, ns, max(5, args.steps // 2), 3, False)
-            ms_u, _, _ = time_steps(st_unfused, ns, max(5, args.steps // 2), 3, False)
+            ms_f, _, _, _ = time_blocks(st_fused, ns, max(5, args.steps // 2), 3, False, args.min_seconds / 2)
+            ms_u, _, _, _ = time_blocks(st_unfused, ns, max(5, args.steps // 2), 3, False, args.min_seconds / 4)
             others[args.workload + "+skip_gate"] = {
                 "tokens_per_s": c["b"] * c["s"] / (ms_f * 1e-3), "ms_per_step": ms_f,
                 "hbm_frac_of_measured": sb / (ms_f * 1e-3) / 1e9 / peak,
@@ -472,7 +676,7 @@ def main():
         try:
             c = CONFIGS[args.workload]
             dch = c["h"] * c["p"]
-            wdt = torch.bfloat16 if c["dtype"] == "bf16" else (torch.float16 if c["dtype"] == "f16" else torch.float32)
+            wdt = TDT[c["dtype"]]
             wide = [torch.randn(c["b"], c["s"], 2 * dch + 64, device=dev, dtype=wdt) for _ in range(2)]
             yo = [torch.empty(c["b"], c["s"], dch, device=dev, dtype=wdt) for _ in range(2)]
             cw = torch.randn(dch, 1, 4, device=dev, dtype=wdt)
@@ -481,7 +685,7 @@ def main():
             def st_conv(i):
                 W.conv1d_silu(wide[i][..., :dch], cw, cb, out=yo[i])
 
-            ms_c, _, _ = time_steps(st_conv, 2, max(5, args.steps // 2), 3, False)
+            ms_c, _, _, _ = time_blocks(st_conv, 2, max(5, args.steps // 2), 3, False, args.min_seconds / 4)
             cbytes = 2 * c["b"] * c["s"] * dch * wide[0].element_size()
             others[args.workload + ":conv1d_silu"] = {"ms_per_step": ms_c, "GBps": cbytes / (ms_c * 1e-3) / 1e9,
                                                       "hbm_frac_of_measured": cbytes / (ms_c * 1e-3) / 1e9 / peak}
@@ -490,34 +694,19 @@ def main():
         except Exception as exc:
             others[args.workload + ":conv1d_silu"] = {"error": f"{type(exc).__name__}: {exc}"}
 
-        # The drop-in Model (reference contract: Model / get_init_inputs / get_inputs, model_ref.py:165-229) at the
-        # reference's production layer shape, two layers instead of 24: projections on cuBLAS, conv, core, skip and gate
-        # on this library's kernels.
+        # The whole Model (reference contract: Model / get_init_inputs / get_inputs, model_ref.py:165-229) at the
+        # reference's production configuration, drop-in next to the reference, timed by the reference's harness.
         try:
-            from workloadsuite_b200 import mamba_model as MM
-            init = MM.get_init_inputs()
-            init[1] = 2
-            model = MM.Model(*init).to(dev).eval()
-            xin = [torch.randn(MM.batch_size, MM.seq_length, MM.d_model, device=dev, dtype=torch.float16) for _ in range(2)]
-
-            def st_model(i):
-                with torch.inference_mode():
-                    model(xin[i])
-
-            ms_m, _, _ = time_steps(st_model, 2, max(5, args.steps // 5), 3, False)
-            others["mamba_model_2_layers"] = {"ms_per_step": ms_m, "ms_per_layer": ms_m / 2,
-                                              "tokens_per_s": MM.batch_size * MM.seq_length / (ms_m * 1e-3),
-                                              "shape": "b8 s2048 d_model2048 h128 p64 n128 g8 block64 fp16"}
-            del model, xin
-            torch.cuda.empty_cache()
+            others["mamba_model_24_layers"] = model_through_reference_harness(dev, args.steps)
         except Exception as exc:
-            others["mamba_model_2_layers"] = {"error": f"{type(exc).__name__}: {exc}"}
+            others["mamba_model_24_layers"] = {"error": f"{type(exc).__name__}: {exc}"}
+            torch.cuda.empty_cache()
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:
-            tps, med, sample = cpu_reference_sample(cfg, 3, 1)
-            cpu_baseline = {"value": tps, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+            tps, med, sample, kind = cpu_reference_sample(cfg, 3, 1)
+            cpu_baseline = {"value": tps, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": kind,
                             "sample": sample, "host_cpus": os.cpu_count(), "s_per_sample": med}
         except Exception as exc:
             cpu_baseline = {"value": None, "unit": "tokens/s", "error": f"{type(exc).__name__}: {exc}"}
@@ -527,18 +716,20 @@ def main():
             "metric": "ssd_forward_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": n_gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": cfg["dtype"], "data": "synthetic",
-            "config": {"workload": WORKLOAD_NAMES[args.workload], "name": args.workload,
-                       "parallelism": ("seq%d+allgather" % world) if seq_parallel else ("heads%d" % world),
-                       "l2": f"{nsets} rotating input sets of {set_bytes / 1e6:.0f} MB per GPU (> L2)",
-                       "kernel": kname, "launch": launch_mode, "segments_per_sequence": plan["nsegments"],
-                       "kernel_launches_per_step": launches_per_step[0]},
+            "config": line_config(args.workload, world, seq_parallel),
+            "run": {"l2": f"{nsets} rotating input sets of {set_bytes / 1e6:.0f} MB per GPU (> L2)",
+                    "kernel": kname, "launch": info["launch_mode"], "segments_per_sequence": plan["nsegments"],
+                    "kernel_launches_per_step": info["launches"], "timed_blocks": len(blocks),
+                    "block_ms_min_median_max": [min(blocks), statistics.median(blocks), max(blocks)],
+                    "timed_gpu_seconds": sum(blocks) * 1e-3, "phases_ms": phases},
+            "parity": parity,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind, "frac_of_8TBs": achieved / 8000.0,
-                         "traffic": NCU_TRAFFIC_BYTES.get((args.workload, kname, world)),
+                         "traffic": captured_traffic(args.workload, world),
                          "algorithmic_bytes_per_step_per_gpu": set_bytes, "algorithmic_bytes_whole_job": total_bytes},
             "cpu_baseline": cpu_baseline,
             "e2e": e2e,
-            "gpu_launches": args.steps * launches_per_step[0],
+            "gpu_launches": args.steps * info["launches"],
             "clocks": clocks,
         }
         if others:

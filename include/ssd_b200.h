@@ -37,7 +37,8 @@ enum {
   SSD_ERR_WORKSPACE = -5,      /* workspace missing or smaller than ssd_b200_workspace_bytes() */
   SSD_ERR_CUDA = -6,           /* a CUDA runtime call failed (launch, attribute) */
   SSD_ERR_MISALIGNED = -7,     /* pointer or stride not aligned as the chosen kernel needs */
-  SSD_ERR_TOO_LARGE = -8       /* size beyond a stated fixed limit */
+  SSD_ERR_TOO_LARGE = -8,      /* size beyond a stated fixed limit */
+  SSD_ERR_DEVICE_WAIT = -9     /* (host-buffer entry, which synchronises) a bounded device-side wait ran out */
 };
 
 enum { SSD_DTYPE_F32 = 0, SSD_DTYPE_F16 = 1, SSD_DTYPE_BF16 = 2 };
@@ -56,8 +57,12 @@ enum {
                                  results of the previous call on this stream with SSD_FLAG_STATE_ONLY, the same
                                  tensors, sizes and nsegments; do not recompute them (a sequence-sharded
                                  forward runs state-only first, exchanges states, then runs with this flag) */
-  SSD_FLAG_SEPARATE_EPILOGUE = 4 /* apply D / Z with the stand-alone epilogue kernel even where the main kernel
+  SSD_FLAG_SEPARATE_EPILOGUE = 4,/* apply D / Z with the stand-alone epilogue kernel even where the main kernel
                                     could fuse them (for comparisons) */
+  SSD_FLAG_INJECT_LOST_HANDOVER = 8 /* testing the give-up path: in a launch whose sequences are handed from CTA to
+                                    CTA, the first CTA leaves without working, so the CTA that continues its
+                                    sequence runs into the bound of its wait (wait_limit_ms), reports status 6 and
+                                    returns; Y and the states of that launch are then incomplete */
 };
 
 /*
@@ -75,7 +80,9 @@ typedef struct SsdArgs {
   const void*  B;               /* [b,s,g,n]  dtype          :126 */
   const void*  C;               /* [b,s,g,n]  dtype          :127 */
   const void*  dt;              /* [b,s,h]    dtype, or NULL for dt == 1   :128,144 */
-  const float* initial_state;   /* [b,h,n,p]  fp32 contiguous, or NULL for zeros :153 */
+  const float* initial_state;   /* [b,h,n,p]  fp32 contiguous, or NULL for zeros :153 (16-byte aligned for the
+                                   tensor-core kernel: SSD_KERNEL_AUTO takes the fp32 scan otherwise, an explicit
+                                   SSD_KERNEL_TCGEN05 returns SSD_ERR_MISALIGNED; the same for final_state) */
   void*        Y;               /* [b,s,h,p]  dtype          :162 (NULL allowed with SSD_FLAG_STATE_ONLY) */
   float*       final_state;     /* [b,h,n,p]  fp32 contiguous, or NULL (the carry after the last chunk, :156) */
   float*       final_logdecay;  /* [b,h]      fp32 sum of A over the sequence, or NULL */
@@ -89,7 +96,8 @@ typedef struct SsdArgs {
   int32_t flags;                /* SSD_FLAG_* */
   int32_t nsegments;            /* 0 = choose; >0 = split each sequence into this many independently
                                    scanned segments joined by a state fold (needs workspace) */
-  int32_t reserved0;
+  int32_t wait_limit_ms;        /* bound of every device-side wait (a kernel that runs into it writes its code to
+                                   `status` and returns); 0 = the default, about one second */
   int64_t x_stride[3];          /* b, s, h */
   int64_t a_stride[3];          /* b, s, h */
   int64_t b_stride[3];          /* b, s, g */
@@ -126,7 +134,9 @@ const char* ssd_b200_kernel_name(const SsdArgs* args);
  * Returns SSD_OK or the validation error.  No reference counterpart. */
 int ssd_b200_plan(const SsdArgs* args, int32_t* kernel, int32_t* nsegments, int32_t* launches);
 
-/* The SSD forward: replaces SSDLayer._ssd_core, model_ref.py:123-162
+/* (A Z whose address or strides are not multiples of 16 bytes is applied by the stand-alone epilogue kernel.)
+ *
+ * The SSD forward: replaces SSDLayer._ssd_core, model_ref.py:123-162
  * (in-chunk prefix sum :135, decay mask :139-141, C.B^T :143, Y_diag :145,
  * chunk states :148-150, inter-chunk recurrence :152-157, Y_off :160-161,
  * sum :162), plus the GQA broadcast of :97-99, the X*dt product of :144 and,
@@ -175,8 +185,10 @@ int ssd_b200_dt_prologue(const void* dt_raw, int64_t stride_b, int64_t stride_l,
  * host pointer (pinned memory gives the best rate), tensors contiguous; strides
  * in `host` are ignored.  `dev_scratch` is a caller-owned DEVICE buffer of at
  * least ssd_b200_host_scratch_bytes() bytes.  Synchronises the host before
- * returning.  Stands in for calling the reference module with CPU tensors
- * (bench.py:217-233 builds inputs on the default device and calls Model). */
+ * returning.  `host->status`, when given, is a HOST int32 that receives the device status word; a non-zero
+ * word also makes the call return SSD_ERR_DEVICE_WAIT.  Unlike the other entry points this one creates (and
+ * destroys) three CUDA streams and a few events per call.  Stands in for calling the reference module with
+ * CPU tensors (bench.py:217-233 builds inputs on the default device and calls Model). */
 size_t ssd_b200_host_scratch_bytes(const SsdArgs* host);
 int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scratch_bytes);
 
@@ -199,10 +211,12 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
  *   - The first call on each device looks the array's device address up (with
  *     that device current) and keeps it; make that first call outside any
  *     stream capture.
- *   - All calls on one device share the array.  It keeps the previous call's
- *     contents; the scan overwrites what it reads, so nothing needs clearing.
- *     Two calls whose kernels may overlap on the GPU (different streams) race
- *     on it: serialise them.
+ *   - All calls on one device share the array, and it keeps the previous call's
+ *     contents.  The two-pass scan writes every segment state before it reads it;
+ *     the single-launch (chained) scan needs its ready flags at zero, and the
+ *     forward clears them itself with a memset on `stream` ahead of the kernel.
+ *     The caller clears nothing.  Two calls whose kernels may overlap on the GPU
+ *     (different streams) race on the array: serialise them.
  * ssd_b200_static_scratch_capacity() returns SSD_STATIC_SCRATCH_BYTES. */
 size_t ssd_b200_static_scratch_capacity(void);
 int ssd_b200_forward_static_scratch(const SsdArgs* args, void* stream);

@@ -64,6 +64,58 @@ def test_kernel_choice_and_workspace_queries(lib):
     assert lib.ssd_b200_fold_states(None, 0, None, 0, None, None, 2, 1, 4, 4, None) == -1
 
 
+def test_misaligned_states_and_bad_wait_limit_are_rejected_on_the_host(lib):
+    """The tensor-core kernels move the fp32 states as 16-byte vectors: a state pointer that is only 4-byte aligned
+    must come back as an error code (explicit kernel) or take the fp32 scan (automatic choice), never reach a
+    kernel.  No device is touched: the pointers are made-up numbers."""
+    a = _shape(2, 256, 4, 64, 128, 1, 128, _lib.DTYPE_BF16)
+    a.X, a.A, a.B, a.C, a.Y = 0x10000, 0x20000, 0x30000, 0x40000, 0x50000
+    assert lib.ssd_b200_kernel_name(C.byref(a)) == b"tcgen05"
+    a.initial_state = 0x60004
+    assert lib.ssd_b200_kernel_name(C.byref(a)) == b"scan_f32"             # automatic choice avoids the vector path
+    a.kernel = _lib.KERNEL_TCGEN05
+    assert lib.ssd_b200_forward(C.byref(a), None) == -7                     # SSD_ERR_MISALIGNED
+    a.initial_state, a.final_state = 0x60000, 0x70008
+    assert lib.ssd_b200_forward(C.byref(a), None) == -7
+    b = _shape(2, 256, 4, 64, 128, 1, 128, _lib.DTYPE_BF16)
+    b.wait_limit_ms = -1
+    assert lib.ssd_b200_forward(C.byref(b), None) == -2
+    assert b"wait" in lib.ssd_b200_strerror(-9)
+
+
+def test_chained_scratch_is_sized_by_hand_over_slots(lib):
+    """One launch with sequences handed from CTA to CTA needs one slot per CTA and head of the pair, whatever the
+    number of sequences: config 2 fits the 16 MiB of the allocation-free entry point."""
+    need = lib.ssd_b200_workspace_bytes(C.byref(_shape(4, 8192, 80, 64, 128, 1, 256, _lib.DTYPE_BF16)))
+    assert 2 * 148 * 128 * 64 * 4 <= need < (16 << 20)
+    assert need == lib.ssd_b200_workspace_bytes(C.byref(_shape(8, 8192, 80, 64, 128, 1, 256, _lib.DTYPE_BF16)))
+
+
+def test_python_wrappers_validate_devices_and_out_before_any_pointer_is_used():
+    import torch
+
+    from workloadsuite_b200 import ssd
+
+    x = torch.zeros(1, 64, 2, 64)
+    other = torch.zeros(1, 64, 2, device="meta")
+    with pytest.raises(ValueError, match="share one device"):
+        ssd._same_device(x, A=other)
+    ssd._same_device(x, A=torch.zeros(1, 64, 2), dt=None)
+    with pytest.raises(ValueError, match="shape"):
+        ssd._check_out(torch.zeros(1, 64, 2, 32), x)
+    with pytest.raises(ValueError, match="shape"):
+        ssd._check_out(torch.zeros(1, 64, 2, 64, dtype=torch.float16), x)
+    with pytest.raises(ValueError, match="innermost"):
+        ssd._check_out(torch.zeros(1, 64, 64, 2).transpose(2, 3), x)
+    ssd._check_out(torch.zeros(1, 64, 4, 64)[:, :, ::2], x)                   # a strided view of rows is fine
+    # the reference block's X: sequence-contiguous, channel-strided (model_ref.py:83-89) -> copied into rows once
+    xt = torch.zeros(1, 2 * 64, 64).transpose(1, 2).unflatten(-1, (2, 64))
+    assert xt.stride(-1) != 1 and ssd._rows_contiguous(xt).stride(-1) == 1
+    assert ssd._rows_contiguous(x) is x
+    with pytest.raises(ValueError, match="share one device"):
+        ssd._check(x, other, torch.zeros(1, 64, 1, 16), torch.zeros(1, 64, 1, 16), None, None)
+
+
 def test_python_api_has_no_cpu_path():
     import torch
 

@@ -68,6 +68,48 @@ def test_sequence_sharded_matches_unsharded(world, with_init):
     assert max(e for _, e in res) < 1e-5, res
 
 
+def _withholding_worker(rank, world, port, q):
+    """Rank 1 scans its shard but never joins the exchange (it leaves between steps, nothing of its in flight)."""
+    import datetime
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    torch.set_num_threads(1)
+    inp = O.make_inputs(b=1, s=64 * world, h=2, p=8, n=6, g=1, dtype=torch.float32, seed=8, decay_scale=0.02)
+    sl = slice(64 * rank, 64 * (rank + 1))
+    def report(msg):
+        q.put((rank, msg))
+        q.close()
+        q.join_thread()                  # the message is in the pipe before the process ends
+        os._exit(0)                      # no destroy_process_group: a peer must find out by itself
+
+    if rank == 1:
+        report("left")
+    eng = sharded.SequenceShardedSSD(scan_fn=_oracle_scan, fold_fn=_oracle_fold)
+    try:
+        eng.forward(inp["X"][:, sl], inp["A"][:, sl], inp["B"][:, sl], inp["C"][:, sl], 32)
+        msg = "no error"
+    except Exception as exc:             # the collective fails: by its timeout, or at once on the closed connection
+        msg = "error: " + type(exc).__name__
+    report(msg)
+
+
+def test_a_rank_that_withholds_its_state_ends_the_exchange_with_an_error():
+    """Failure detection on the host: the sequence-sharded forward has one collective; when a rank never joins it,
+    the others must get an exception from that collective (a short process-group timeout), not a result."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_withholding_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+    assert res[1] == "left"
+    assert res[0].startswith("error"), res
+
+
 def test_head_shard_bounds_cover_all_heads_and_keep_groups_whole():
     for h, g, world in [(80, 1, 8), (80, 1, 4), (48, 8, 8), (48, 8, 2), (128, 8, 4), (24, 1, 2)]:
         seen = []

@@ -328,6 +328,193 @@ def test_full_size_properties(name):
     assert per_bh < 2e-2 and fro < 5e-3, (per_bh, fro)
 
 
+def _check_sampled_units(Y, inp, units, H=None, tol=2e-2):
+    """Sampled (batch, head) units of a full-size run against the float64 recurrence (one oracle call per batch
+    entry, all its sampled heads at once)."""
+    h, g = inp["X"].shape[2], inp["B"].shape[2]
+    by_batch = {}
+    for bi, hi in units:
+        by_batch.setdefault(bi, []).append(hi)
+    for bi, heads in by_batch.items():
+        hs = torch.tensor(heads)
+        gs = hs // (h // g)
+        init = inp["initial_states"][bi:bi + 1, hs] if "initial_states" in inp else None
+        # one oracle head per sampled head, each with the B/C of its own group (model_ref.py:97-99)
+        Yr, Hr = O.ssd_recurrence(inp["X"][bi:bi + 1, :, hs], inp["A"][bi:bi + 1, :, hs], inp["B"][bi:bi + 1, :, gs],
+                                  inp["C"][bi:bi + 1, :, gs], initial_states=init, return_final_state=True)
+        per_bh, fro = O.error_metrics(Y[bi:bi + 1, :, hs.to(Y.device)].cpu(), Yr)
+        assert per_bh < tol and fro < tol, (bi, heads, per_bh, fro)
+        if H is not None:
+            Hg = H[bi:bi + 1, hs.to(H.device)].cpu().double()
+            herr = ((Hg - Hr).abs().amax(dim=(2, 3)) / Hr.abs().amax(dim=(2, 3)).clamp_min(1e-30)).max().item()
+            assert herr < tol, ("final state", bi, heads, herr)
+
+
+@pytest.mark.parametrize("decay_scale", [1.0, 0.02])
+def test_full_size_config3_long_sequence(decay_scale):
+    """Config 3 at its stated size (one sequence of 131 072 tokens, 32 heads: 1 024 tiles per sequence, cut into
+    segments by the default plan): first, last and two middle heads against the float64 recurrence over all tokens,
+    with the configuration's own decays and with slow decays (so that what crosses the segment cuts matters), plus
+    the final state."""
+    W = _ssd()
+    cfg, inp = _full("cfg3", seed=3)
+    if decay_scale != 1.0:
+        inp["A"] = inp["A"] * decay_scale
+    d = _to_dev(inp)
+    plan = W.plan(d["X"], d["A"], d["B"], d["C"], cfg["chunk"])
+    assert plan["nsegments"] >= 9 and plan["kernel"] == "tcgen05"
+    Y, H = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], cfg["chunk"], return_final_state=True)
+    torch.cuda.synchronize()
+    assert torch.isfinite(Y).all() and torch.isfinite(H).all()
+    _check_sampled_units(Y, inp, [(0, 0), (0, 13), (0, 18), (0, cfg["h"] - 1)], H=H)
+
+
+def test_full_size_config4_many_short_sequences_with_initial_states():
+    """Config 4 at its stated size (256 x 48 units of 512 tokens, 8 B/C groups of 6 heads, d_state 64, fp32 initial
+    states [256,48,64,64]): first, last and middle units, heads of different groups, Y and final state."""
+    W = _ssd()
+    cfg, inp = _full("cfg4", seed=4)
+    assert inp["initial_states"].shape == (256, 48, 64, 64) and inp["B"].shape[2] == 8
+    d = _to_dev(inp)
+    Y, H = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], cfg["chunk"], initial_states=d["initial_states"],
+                         return_final_state=True)
+    torch.cuda.synchronize()
+    assert torch.isfinite(Y).all() and torch.isfinite(H).all()
+    units = [(0, 0), (0, 5), (0, 6), (255, 47), (255, 41), (128, 20), (77, 7), (3, 30)]   # groups 0, 1, 3, 5, 6, 7
+    _check_sampled_units(Y, inp, units, H=H)
+    # the same with slow decays: the initial state then reaches every token of the 512
+    inp2 = dict(inp)
+    inp2["A"] = inp["A"] * 0.02
+    Y2, H2 = W.ssd_forward(d["X"], inp2["A"].to(DEV), d["B"], d["C"], cfg["chunk"], initial_states=d["initial_states"],
+                           return_final_state=True)
+    _check_sampled_units(Y2, inp2, [(0, 0), (255, 47), (100, 11)], H=H2)
+
+
+# ---------------------------------------------------------------- the reference-side binding and the give-up path
+
+def _integration_snippet():
+    """The replacement body of ``SSDLayer._ssd_core`` exactly as INTEGRATION.md prints it."""
+    import re
+    from pathlib import Path
+
+    text = (Path(__file__).resolve().parent.parent / "INTEGRATION.md").read_text()
+    m = re.search(r"```python\n(from workloadsuite_b200 import ssd_forward\n.*?)```", text, re.S)
+    assert m, "the binding snippet is missing from INTEGRATION.md"
+    ns = {}
+    exec(m.group(1), ns)
+    return ns["_ssd_core"]
+
+
+def test_reference_binding_accepts_the_reference_layers_own_layout():
+    """``SSDLayer.forward`` hands ``_ssd_core`` an X that is sequence-contiguous and channel-strided (a permuted
+    [b, d, l] tensor, model_ref.py:83-89,106) and B/C repeated to heads (:97-99).  The binding of INTEGRATION.md,
+    run verbatim on tensors laid out that way, must equal the call on contiguous tensors."""
+    W = _ssd()
+    core = _integration_snippet()
+    b, s, h, p, n, l = 2, 512, 4, 64, 128, 64
+    inp = O.make_inputs(b=b, s=s, h=h, p=p, n=n, g=h, dtype=torch.float16, seed=51, decay_scale=0.1)
+    d = _to_dev(inp)
+    x_bdl = d["X"].reshape(b, s, h * p).transpose(1, 2).contiguous()            # [b, d, l], what the conv produces
+    X = x_bdl.transpose(1, 2).view(b, s, h, p)                                   # rearrange "b d l -> b l d", :86-89
+    assert X.stride() == (h * p * s, 1, p * s, s) and torch.equal(X, d["X"])
+    dt = (0.5 + torch.rand(b, s, h, device=DEV)).half()
+    c = s // l
+    Y = core(None, X.reshape(b, c, l, h, p), d["B"].reshape(b, c, l, h, n), d["C"].reshape(b, c, l, h, n),
+             dt.reshape(b, c, l, h), d["A"].reshape(b, c, l, h), b)
+    want = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], l, dt=dt)
+    assert Y.shape == (b, c, l, h, p) and torch.equal(Y.reshape(b, s, h, p), want)
+    Yr = O.ssd_recurrence(inp["X"], inp["A"], inp["B"], inp["C"], dt=dt.cpu())
+    assert max(O.error_metrics(want.cpu(), Yr)) < 2e-2
+
+
+def test_reference_layer_with_the_binding_patched_in():
+    """The unmodified reference ``SSDLayer`` (bytecode under oracle/_ref, when it was built) with only ``_ssd_core``
+    replaced by the binding of INTEGRATION.md, against the same layer untouched, both on the GPU in fp16."""
+    from oracle import build_ref as R
+
+    mod = R.load_model_ref()
+    if mod is None:
+        pytest.skip("oracle/_ref was not built on this machine")
+    core = _integration_snippet()
+    torch.manual_seed(7)
+    layer = mod.SSDLayer(d_model=256, n_heads=8, d_state=128, d_head=64, n_groups=2, block_len=64).to(DEV).eval()
+    u = torch.randn(2, 512, 256, dtype=torch.float16, device=DEV)
+    with torch.inference_mode():
+        ref = layer(u)
+        layer._ssd_core = core.__get__(layer)
+        got = layer(u)
+    err = ((got.double() - ref.double()).abs().max() / ref.double().abs().max()).item()
+    assert err < 2e-2, err
+
+
+def test_torch_compile_contract_of_the_dropin_model():
+    """The reference harness compiles the very model instance it timed (bench.py:185: fullgraph=False) and the
+    reference's tests check compiled == eager with the eager backend (tests/test_diverse_workloads.py:74-83)."""
+    from workloadsuite_b200 import mamba_model as M
+
+    torch.manual_seed(3)
+    model = M.Model(128, 2, 4, 128, 64, 2, 64, 4).to(DEV).eval()
+    x = torch.randn(2, 256, 128, dtype=torch.float16, device=DEV)
+    try:
+        with torch.inference_mode():
+            want = model(x)
+            compiled = torch.compile(model, backend="eager", fullgraph=False)
+            got = compiled(x)
+            got2 = compiled(x)
+        assert torch.equal(got, want) and torch.equal(got2, want)
+    finally:
+        torch._dynamo.reset()
+
+
+def test_gate_whose_rows_are_not_16_byte_aligned_takes_the_standalone_epilogue():
+    W = _ssd()
+    inp = O.make_inputs(b=1, s=256, h=4, p=64, n=128, g=1, dtype=torch.bfloat16, seed=52, decay_scale=0.05)
+    d = _to_dev(inp)
+    gen = torch.Generator().manual_seed(53)
+    z = torch.randn(1, 256, 4, 64, generator=gen).bfloat16()
+    D = torch.randn(4, generator=gen)
+    buf = torch.zeros(z.numel() + 1, dtype=torch.bfloat16, device=DEV)
+    zv = buf[1:].view(1, 256, 4, 64)                # same strides, address off by one element
+    zv.copy_(z)
+    assert zv.data_ptr() % 16 != 0
+    Y = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], 128, D=D.to(DEV), z=zv)
+    Y2 = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], 128, D=D.to(DEV), z=z.to(DEV), separate_epilogue=True)
+    assert torch.equal(Y, Y2)
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_next_forward_is_fine():
+    """Every device-side wait is bounded.  Here one is made to run out: in a launch whose sequences are handed from
+    CTA to CTA, the first CTA leaves without publishing (``inject_lost_handover``), so the CTA that continues its
+    sequence waits -- for 3 ms instead of the default second -- gives up, every role of that CTA leaves, tensor
+    memory is freed, the kernel returns by itself and the status word reads 6.  The context stays usable: the same
+    forward without the injection is then correct."""
+    import time
+
+    if not _tc_available():
+        pytest.skip("tensor-core kernel not available")
+    W = _ssd()
+    # 200 head pairs x 4 tiles over 148 CTAs: the first CTA gets tiles 0..4, i.e. one whole sequence and the first
+    # tile of the next, whose remaining tiles wait on the second CTA for a state that never comes
+    inp = O.make_inputs(b=50, s=512, h=8, p=64, n=128, g=2, dtype=torch.bfloat16, seed=54, decay_scale=0.05)
+    d = _to_dev(inp)
+    assert W.plan(d["X"], d["A"], d["B"], d["C"], 256, nsegments=2)["launches"] == 1      # chained
+    W.ssd_forward(d["X"], d["A"], d["B"], d["C"], 256, nsegments=2)                       # warm
+    assert W.device_status(DEV) == 0
+    t0 = time.perf_counter()
+    W.ssd_forward(d["X"], d["A"], d["B"], d["C"], 256, nsegments=2, wait_limit_ms=3, inject_lost_handover=True)
+    torch.cuda.synchronize()
+    took = time.perf_counter() - t0
+    assert W.device_status(DEV) == 6                 # STATUS_WAIT_TIMEOUT_CHAIN; the call above cleared the word
+    assert took < 0.5, took                          # it gave up after milliseconds, not after the default second
+    Y = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], 256, nsegments=2)
+    torch.cuda.synchronize()
+    assert W.device_status(DEV) == 0
+    Yr = O.ssd_recurrence(inp["X"][:2], inp["A"][:2], inp["B"][:2], inp["C"][:2])
+    assert max(O.error_metrics(Y[:2].cpu(), Yr)) < 2e-2
+    Yl = O.ssd_recurrence(inp["X"][-1:], inp["A"][-1:], inp["B"][-1:], inp["C"][-1:])
+    assert max(O.error_metrics(Y[-1:].cpu(), Yl)) < 2e-2
+
+
 # ---------------------------------------------------------------- host-buffer entry point and the drop-in Model
 
 @pytest.mark.parametrize("case", ["pairs_bf16", "pairs_fp16_dt_segmented", "chained_bf16_dt", "single_heads_fp16", "fp32_simt",

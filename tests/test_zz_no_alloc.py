@@ -23,12 +23,12 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _call_static(lib, W, d, chunk, nsegments, Y):
+def _call_static(lib, W, d, chunk, nsegments, Y, kernel="scan_f32"):
     from workloadsuite_b200 import _lib
     from workloadsuite_b200.ssd import _fill
 
     args = _lib.SsdArgs()
-    _fill(args, d["X"], d["A"], d["B"], d["C"], None, d.get("initial_states"), Y, None, None, chunk, "scan_f32",
+    _fill(args, d["X"], d["A"], d["B"], d["C"], None, d.get("initial_states"), Y, None, None, chunk, kernel,
           nsegments, False)
     assert args.workspace is None and args.workspace_bytes == 0     # the caller passes no scratch
     with torch.cuda.device(Y.device):
@@ -59,6 +59,38 @@ def test_static_scratch_entry_matches_workspace_entry_twice():
             # and both agree with the definition
             Yr = O.ssd_recurrence(inp["X"], inp["A"], inp["B"], inp["C"], initial_states=inp["initial_states"])
             assert O.error_metrics(got.cpu(), Yr)[0] < tol
+
+
+@pytest.mark.parametrize("mode", ["two_pass", "chained"])
+def test_static_scratch_entry_with_the_tensor_core_kernels_twice(mode):
+    """The tensor-core kernels use the shared array in two ways: the two-pass scan keeps per-segment states in it,
+    the single-launch scan hands states from CTA to CTA through it and needs its ready flags cleared (the entry
+    point does that itself).  Two calls in a row on different data, against the ordinary entry point."""
+    import workloadsuite_b200 as W
+    from workloadsuite_b200 import _lib
+
+    lib = _lib.load()
+    if mode == "two_pass":      # 8 head pairs for 148 SMs: segments scanned concurrently, then folded
+        shape, nseg = dict(b=2, s=2048, h=4, p=64, n=128, g=1), 4
+    else:                       # 160 head pairs: tiles dealt out evenly inside one launch
+        shape, nseg = dict(b=40, s=512, h=8, p=64, n=128, g=2), 2
+    for seed in (61, 62):
+        inp = O.make_inputs(dtype=torch.bfloat16, init=True, seed=seed, decay_scale=0.02, **shape)
+        d = {k: v.to(DEV) for k, v in inp.items()}
+        plan = W.plan(d["X"], d["A"], d["B"], d["C"], 256, kernel="tcgen05", nsegments=nseg)
+        assert plan["launches"] == (3 if mode == "two_pass" else 1) and 0 < plan["workspace_bytes"] <= 16 << 20
+        want = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], 256, initial_states=d["initial_states"],
+                             kernel="tcgen05", nsegments=nseg)
+        got = torch.empty_like(want)
+        rc = _call_static(lib, W, d, 256, nseg, got, kernel="tcgen05")
+        assert rc == 0, _lib.strerror(rc)
+        torch.cuda.synchronize()
+        assert W.device_status(DEV) == 0
+        per_bh, fro = O.error_metrics(got.cpu(), want.cpu())
+        assert per_bh < 2e-2 and fro < 2e-2, (mode, seed, per_bh, fro)
+        Yr = O.ssd_recurrence(inp["X"][:1], inp["A"][:1], inp["B"][:1], inp["C"][:1],
+                              initial_states=inp["initial_states"][:1])
+        assert O.error_metrics(got[:1].cpu(), Yr)[0] < 2e-2
 
 
 def test_static_scratch_entry_rejects_oversized_problems():

@@ -11,18 +11,20 @@ from pathlib import Path
 
 from . import build as _build
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 SSD_OK = 0
 ERRORS = {
     -1: "SSD_ERR_NULL_POINTER", -2: "SSD_ERR_BAD_SHAPE", -3: "SSD_ERR_BAD_CHUNK", -4: "SSD_ERR_UNSUPPORTED",
     -5: "SSD_ERR_WORKSPACE", -6: "SSD_ERR_CUDA", -7: "SSD_ERR_MISALIGNED", -8: "SSD_ERR_TOO_LARGE",
+    -9: "SSD_ERR_DEVICE_WAIT",
 }
 DTYPE_F32, DTYPE_F16, DTYPE_BF16 = 0, 1, 2
 KERNEL_AUTO, KERNEL_SCAN_F32, KERNEL_TCGEN05 = 0, 1, 2
 FLAG_STATE_ONLY = 1
 FLAG_REUSE_SEGMENTS = 2
 FLAG_SEPARATE_EPILOGUE = 4
+FLAG_INJECT_LOST_HANDOVER = 8
 
 # every symbol include/ssd_b200.h declares
 EXPORTS = (
@@ -43,7 +45,7 @@ class SsdArgs(C.Structure):
         ("status", C.c_void_p),
         ("batch", C.c_int32), ("seqlen", C.c_int32), ("nheads", C.c_int32), ("headdim", C.c_int32),
         ("dstate", C.c_int32), ("ngroups", C.c_int32), ("chunk", C.c_int32), ("dtype", C.c_int32),
-        ("kernel", C.c_int32), ("flags", C.c_int32), ("nsegments", C.c_int32), ("reserved0", C.c_int32),
+        ("kernel", C.c_int32), ("flags", C.c_int32), ("nsegments", C.c_int32), ("wait_limit_ms", C.c_int32),
         ("x_stride", C.c_int64 * 3), ("a_stride", C.c_int64 * 3), ("b_stride", C.c_int64 * 3),
         ("c_stride", C.c_int64 * 3), ("dt_stride", C.c_int64 * 3), ("y_stride", C.c_int64 * 3),
         ("D", C.c_void_p), ("Z", C.c_void_p), ("z_stride", C.c_int64 * 3),
@@ -63,10 +65,11 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     if _LIB is not None:
         return _LIB
     path = lib_path()
-    if not path.exists() or (os.environ.get("SSD_B200_REBUILD") == "1"):
+    if not path.exists() or not _build.is_current() or os.environ.get("SSD_B200_REBUILD") == "1":
+        # missing, or built from other sources than the ones beside it: never run a stale binary
         if not build_if_missing:
-            raise RuntimeError(f"{path} is missing; run `python -m workloadsuite_b200.build`")
-        _build.build()
+            raise RuntimeError(f"{path} is missing or stale; run `python -m workloadsuite_b200.build`")
+        _build.build(force=os.environ.get("SSD_B200_REBUILD") == "1")
     lib = C.CDLL(str(path))
     lib.ssd_b200_abi_version.restype = C.c_int
     lib.ssd_b200_strerror.restype = C.c_char_p

@@ -50,6 +50,12 @@ def _fingerprint() -> str:
     return h.hexdigest()
 
 
+def source_fingerprint() -> str:
+    """Hash of the CUDA sources, the public header and the compiler flags (what the shipped library was built from
+    when ``is_current()``)."""
+    return _fingerprint()
+
+
 def is_current() -> bool:
     return LIB.exists() and STAMP.exists() and STAMP.read_text().strip() == _fingerprint()
 

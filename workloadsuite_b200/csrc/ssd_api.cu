@@ -9,7 +9,7 @@
 
 namespace {
 
-constexpr int kAbiVersion = 2;
+constexpr int kAbiVersion = 3;
 constexpr int kSmCount = 148;  // B200
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -26,7 +26,7 @@ int validate(const SsdArgs* a) {
     return SSD_ERR_UNSUPPORTED;
   if (a->kernel != SSD_KERNEL_AUTO && a->kernel != SSD_KERNEL_SCAN_F32 && a->kernel != SSD_KERNEL_TCGEN05)
     return SSD_ERR_UNSUPPORTED;
-  if (a->nsegments < 0) return SSD_ERR_BAD_SHAPE;
+  if (a->nsegments < 0 || a->wait_limit_ms < 0) return SSD_ERR_BAD_SHAPE;
   if ((int64_t)a->batch * a->nheads > 0x7fffffffLL) return SSD_ERR_TOO_LARGE;
   return SSD_OK;
 }
@@ -39,18 +39,18 @@ int validate_pointers(const SsdArgs* a) {
   return SSD_OK;
 }
 
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 int resolve_kernel(const SsdArgs* a) {
   if (a->kernel == SSD_KERNEL_SCAN_F32) return SSD_KERNEL_SCAN_F32;
   if (a->kernel == SSD_KERNEL_TCGEN05) return SSD_KERNEL_TCGEN05;
-  return ssd::tc_supports(*a) ? SSD_KERNEL_TCGEN05 : SSD_KERNEL_SCAN_F32;
+  // (states that are only 4-byte aligned go to the fp32 scan, which moves them element by element)
+  const bool st16 = aligned16(a->initial_state) && aligned16(a->final_state);
+  return ssd::tc_supports(*a) && st16 ? SSD_KERNEL_TCGEN05 : SSD_KERNEL_SCAN_F32;
 }
 
-// SSD_B200_TC_VARIANT=1 forces the one-head-per-CTA tensor-core kernel (for comparisons).
-bool use_tc2(const SsdArgs* a) {
-  const char* v = std::getenv("SSD_B200_TC_VARIANT");
-  if (v && v[0] == '1') return false;
-  return ssd::tc2_supports(*a);
-}
+// The two-head kernel whenever the heads of a B/C group come in pairs, else one head per CTA.
+bool use_tc2(const SsdArgs* a) { return ssd::tc2_supports(*a); }
 
 int tile_tokens(int kernel) { return kernel == SSD_KERNEL_TCGEN05 ? 128 : ssd::scan_f32_tile_tokens(); }
 
@@ -77,8 +77,6 @@ void resolve_segments(const SsdArgs* a, int kernel, int* nseg, int* seg_len) {
   *nseg = (a->seqlen + len - 1) / len;
 }
 
-bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
-
 bool strides_mult(const int64_t* s, int m) { return s[0] % m == 0 && s[1] % m == 0 && s[2] % m == 0; }
 
 void fill_params(const SsdArgs* a, ssd::ScanParams* p) {
@@ -100,7 +98,20 @@ void fill_params(const SsdArgs* a, ssd::ScanParams* p) {
   if (a->Y) v = v && aligned16(a->Y) && strides_mult(a->y_stride, per16);
   if (a->Z) v = v && aligned16(a->Z) && strides_mult(a->z_stride, per16);
   p->vec_ok = v ? 1 : 0;
+  // the bound of the device-side waits: about a second by default; SM clocks run at up to ~2 GHz
+  p->wait_clocks = a->wait_limit_ms > 0 ? (long long)a->wait_limit_ms * 2000000LL : 2000000000LL;
+  p->inject_lost_handover = (a->flags & SSD_FLAG_INJECT_LOST_HANDOVER) ? 1 : 0;
 }
+
+// The gate rows are read with 16-byte loads by the fused epilogue; the stand-alone kernel has a scalar path.
+bool z_vector_friendly(const SsdArgs* a) {
+  if (!a->Z) return true;
+  const int per16 = 16 / elem_size(a->dtype);
+  return aligned16(a->Z) && strides_mult(a->z_stride, per16);
+}
+
+// The tensor-core kernels move the fp32 states as 16-byte vectors.
+bool states_aligned16(const SsdArgs* a) { return aligned16(a->initial_state) && aligned16(a->final_state); }
 
 int launch_kernel(int kernel, const SsdArgs* a, const ssd::ScanParams& prm, cudaStream_t stream) {
   if (kernel == SSD_KERNEL_TCGEN05) return use_tc2(a) ? ssd::launch_tc2(*a, prm, stream) : ssd::launch_tc(*a, prm, stream);
@@ -124,6 +135,7 @@ const char* ssd_b200_strerror(int code) {
     case SSD_ERR_CUDA: return "a CUDA runtime call failed";
     case SSD_ERR_MISALIGNED: return "pointer or stride not aligned for the selected kernel";
     case SSD_ERR_TOO_LARGE: return "size beyond a fixed limit";
+    case SSD_ERR_DEVICE_WAIT: return "a bounded device-side wait ran out; the results are incomplete";
     default: return "unknown error code";
   }
 }
@@ -160,9 +172,13 @@ size_t ssd_b200_workspace_bytes(const SsdArgs* args) {
   if (nseg <= 1) return 0;
   const size_t units = (size_t)args->batch * args->nheads;
   const size_t np = (size_t)args->dstate * args->headdim;
-  // zero-start segment states, states entering the segments, segment log-decay sums, and (chained mode) one
-  // ready flag per segment
-  return 2 * align_up(units * nseg * np * sizeof(float), 256) + 2 * align_up(units * nseg * sizeof(float), 256);
+  if (kernel == SSD_KERNEL_TCGEN05 && use_tc2(args) && ssd::tc2_chain_segments(*args, nseg)) {
+    // chained mode: one hand-over slot per CTA and head of the pair -- state, log-decay sum, ready flag
+    const size_t slots = 2 * (size_t)kSmCount;
+    return align_up(slots * np * sizeof(float), 256) + 2 * align_up(slots * sizeof(float), 256);
+  }
+  // two passes: zero-start segment states, states entering the segments, segment log-decay sums
+  return 2 * align_up(units * nseg * np * sizeof(float), 256) + align_up(units * nseg * sizeof(float), 256);
 }
 
 // The forward proper.  `fuse_epilogue`: the selected kernel applies D / Z itself; otherwise they are dropped here
@@ -175,6 +191,7 @@ static int forward_impl(const SsdArgs* args, void* stream_v, bool fuse_epilogue)
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   const int kernel = resolve_kernel(args);
   if (kernel == SSD_KERNEL_TCGEN05 && !ssd::tc_supports(*args)) return SSD_ERR_UNSUPPORTED;
+  if (kernel == SSD_KERNEL_TCGEN05 && !states_aligned16(args)) return SSD_ERR_MISALIGNED;
   if (kernel == SSD_KERNEL_SCAN_F32 && !ssd::scan_f32_supports(args->headdim, args->dstate))
     return SSD_ERR_UNSUPPORTED;
 
@@ -204,21 +221,20 @@ static int forward_impl(const SsdArgs* args, void* stream_v, bool fuse_epilogue)
   const size_t need = ssd_b200_workspace_bytes(args);
   if (!args->workspace || args->workspace_bytes < need) return SSD_ERR_WORKSPACE;
   if (reinterpret_cast<uintptr_t>(args->workspace) & 255) return SSD_ERR_MISALIGNED;
-  float* seg_states = static_cast<float*>(args->workspace);
-  const size_t st_bytes = align_up((size_t)units * nseg * np * sizeof(float), 256);
-  float* seg_in = reinterpret_cast<float*>(static_cast<char*>(args->workspace) + st_bytes);
-  float* seg_ld = reinterpret_cast<float*>(static_cast<char*>(args->workspace) + 2 * st_bytes);
-
   if (kernel == SSD_KERNEL_TCGEN05 && use_tc2(args) && ssd::tc2_chain_segments(*args, nseg)) {
-    // one launch: the segments of a sequence hand their state over through the workspace
-    int32_t* flags = reinterpret_cast<int32_t*>(reinterpret_cast<char*>(seg_ld) +
-                                                align_up((size_t)units * nseg * sizeof(float), 256));
-    if (cudaMemsetAsync(flags, 0, (size_t)units * nseg * sizeof(int32_t), stream) != cudaSuccess) return SSD_ERR_CUDA;
+    // one launch: the pieces of a sequence hand their state over through the workspace, one slot per CTA and head
+    const size_t slots = 2 * (size_t)kSmCount;
+    char* ws = static_cast<char*>(args->workspace);
+    float* slot_state = reinterpret_cast<float*>(ws);
+    float* slot_ld = reinterpret_cast<float*>(ws + align_up(slots * np * sizeof(float), 256));
+    int32_t* flags = reinterpret_cast<int32_t*>(reinterpret_cast<char*>(slot_ld) + align_up(slots * sizeof(float), 256));
+    // the ready flags must start at zero (the workspace keeps the previous call's contents)
+    if (cudaMemsetAsync(flags, 0, slots * sizeof(int32_t), stream) != cudaSuccess) return SSD_ERR_CUDA;
     ssd::ScanParams pc = prm;
     pc.compute_y = state_only ? 0 : 1;
     pc.chain = 1;
-    pc.chain_state = seg_states;
-    pc.chain_ld = seg_ld;
+    pc.chain_state = slot_state;
+    pc.chain_ld = slot_ld;
     pc.chain_flag = flags;
     pc.init = args->initial_state;   // only read by the first segment
     pc.init_unit_stride = np;
@@ -231,6 +247,11 @@ static int forward_impl(const SsdArgs* args, void* stream_v, bool fuse_epilogue)
     pc.finld_seg_stride = 0;
     return launch_kernel(kernel, args, pc, stream);
   }
+
+  float* seg_states = static_cast<float*>(args->workspace);
+  const size_t st_bytes = align_up((size_t)units * nseg * np * sizeof(float), 256);
+  float* seg_in = reinterpret_cast<float*>(static_cast<char*>(args->workspace) + st_bytes);
+  float* seg_ld = reinterpret_cast<float*>(static_cast<char*>(args->workspace) + 2 * st_bytes);
 
   // pass 1: every segment from a zero state, state and log-decay sum only
   if (!(args->flags & SSD_FLAG_REUSE_SEGMENTS)) {
@@ -274,7 +295,7 @@ int ssd_b200_forward(const SsdArgs* args, void* stream_v) {
   // skip and gate of model_ref.py:116-118: fused into the two-head tensor-core kernel, a kernel of their own otherwise
   const int kernel = resolve_kernel(args);
   const bool fuse = kernel == SSD_KERNEL_TCGEN05 && ssd::tc_supports(*args) && use_tc2(args) &&
-                    !(args->flags & SSD_FLAG_SEPARATE_EPILOGUE);
+                    z_vector_friendly(args) && !(args->flags & SSD_FLAG_SEPARATE_EPILOGUE);
   rc = forward_impl(args, stream_v, fuse);
   if (rc != SSD_OK || fuse) return rc;
   ssd::ScanParams ep;

@@ -41,6 +41,8 @@ struct ScanParams {
   int seg_len, nseg;
   int compute_y;
   int vec_ok;          // all row starts 16-byte aligned
+  long long wait_clocks;   // bound of every device-side wait, in SM clock cycles
+  int inject_lost_handover;   // SSD_FLAG_INJECT_LOST_HANDOVER: CTA 0 of a chained launch leaves without working
   // Chained mode (two-head tensor-core kernel only): a piece of a sequence starts from the state that the
   // piece before it (on the neighbouring CTA) left in chain_state, once chain_flag says it is there.
   int chain;

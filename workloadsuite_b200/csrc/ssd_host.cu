@@ -25,7 +25,8 @@ struct Plan {
   int nchunks;     // chunks per batch entry
   int group;       // batch entries per chunk (> 1 only when a whole entry is much smaller than a chunk)
   size_t x_bytes, a_bytes, dt_bytes, bc_bytes, ws_bytes, ld_bytes, st_bytes;   // a, dt, bc: one whole batch entry
-  size_t slot_bytes, entry_bytes, total_bytes;
+  size_t slot_bytes, entry_bytes, ldall_bytes, total_bytes;
+  int nslices;
 };
 
 bool basic_ok(const SsdArgs* a) {
@@ -40,9 +41,14 @@ void chunk_args(const SsdArgs* a, int tokens, int entries, SsdArgs* s) {
   s->batch = entries;
   s->seqlen = tokens;
   s->nsegments = 0;
-  s->status = nullptr;
+  s->status = nullptr;   // (the pipeline points it at the status word inside its device scratch)
   s->D = nullptr;
   s->Z = nullptr;
+  // `a` holds HOST pointers: kernel choice and scratch size must follow the device buffers, which are
+  // 256-byte aligned, so the tensor pointers are cleared here (a shape query) and set by the pipeline
+  s->X = nullptr; s->A = nullptr; s->B = nullptr; s->C = nullptr; s->Y = nullptr;
+  s->initial_state = nullptr; s->final_state = nullptr; s->final_logdecay = nullptr;
+  s->workspace = nullptr; s->workspace_bytes = 0;
   // the chunk's tensors are contiguous in the device buffers (kernel choice and scratch size depend on the strides)
   const int64_t h = a->nheads, p = a->headdim, g = a->ngroups, n = a->dstate;
   const int64_t xs[3] = {tokens * h * p, h * p, p}, as[3] = {tokens * h, h, 1}, bs[3] = {tokens * g * n, g * n, n};
@@ -50,6 +56,47 @@ void chunk_args(const SsdArgs* a, int tokens, int entries, SsdArgs* s) {
     s->x_stride[k] = xs[k]; s->y_stride[k] = xs[k]; s->a_stride[k] = as[k]; s->dt_stride[k] = as[k];
     s->b_stride[k] = bs[k]; s->c_stride[k] = bs[k];
   }
+}
+
+struct Slice { int bi, nb, ci, t0, tokens; bool first, last; };   // nb batch entries from bi on
+
+// The chunks of all batch entries in order.  The first entry opens and the last one closes with a ramp of smaller
+// chunks (1/8, 1/8, 1/4, 1/2 of the regular length), so that the device->host stream starts early and the
+// host->device stream ends late: the two directions then overlap for all but a fraction of a chunk.
+std::vector<Slice> make_slices(const SsdArgs* host, int tokens_per_chunk, int group) {
+  std::vector<Slice> slices;
+  const int b = host->batch, s = host->seqlen;
+  int unit = host->chunk / gcd_int(host->chunk, 128) * 128;
+  if (s % unit != 0) unit = host->chunk;
+  for (int bi = 0; bi < b && group > 1; bi += group)
+    slices.push_back({bi, std::min(group, b - bi), 0, 0, s, true, true});
+  for (int bi = 0; bi < b && group == 1; ++bi) {
+    std::vector<int> lens;
+    int left = s;
+    const int ramp[4] = {tokens_per_chunk / 8, tokens_per_chunk / 8, tokens_per_chunk / 4, tokens_per_chunk / 2};
+    std::vector<int> head, tail;
+    if (bi == 0)
+      for (int k = 0; k < 4; ++k) {
+        const int len = ramp[k] / unit * unit;
+        if (len > 0 && left - len >= tokens_per_chunk) { head.push_back(len); left -= len; }
+      }
+    if (bi == b - 1)
+      for (int k = 0; k < 4; ++k) {
+        const int len = ramp[k] / unit * unit;
+        if (len > 0 && left - len >= tokens_per_chunk) { tail.insert(tail.begin(), len); left -= len; }
+      }
+    lens = head;
+    while (left > 0) { const int len = std::min(tokens_per_chunk, left); lens.push_back(len); left -= len; }
+    // (ramp-down pieces are listed largest first, so that the last copies are the small ones)
+    std::sort(tail.begin(), tail.end(), [](int a, int c) { return a > c; });
+    lens.insert(lens.end(), tail.begin(), tail.end());
+    int t0 = 0;
+    for (size_t k = 0; k < lens.size(); ++k) {
+      slices.push_back({bi, 1, (int)k, t0, lens[k], k == 0, k + 1 == lens.size()});
+      t0 += lens[k];
+    }
+  }
+  return slices;
 }
 
 Plan make_plan(const SsdArgs* a) {
@@ -79,22 +126,26 @@ Plan make_plan(const SsdArgs* a) {
   pl.bc_bytes = align_up(k * a->seqlen * a->ngroups * a->dstate * e, 256);
   pl.ld_bytes = align_up(k * a->nheads * 4, 256);
   pl.st_bytes = align_up(k * a->nheads * a->dstate * a->headdim * 4, 256);
-  SsdArgs s;
-  chunk_args(a, pl.tokens, pl.group, &s);
-  pl.ws_bytes = align_up(ssd_b200_workspace_bytes(&s), 256);
-  if (pl.group > 1 && a->batch % pl.group != 0) {   // the last, smaller group
-    chunk_args(a, pl.tokens, a->batch % pl.group, &s);
+  // scratch of the forward: the largest need over every (entries, tokens) shape the pipeline will launch
+  const std::vector<Slice> slices = make_slices(a, pl.tokens, pl.group);
+  pl.nslices = (int)slices.size();
+  pl.ws_bytes = 0;
+  int seen_nb = -1, seen_tokens = -1;
+  for (const Slice& sl : slices) {
+    if (sl.nb == seen_nb && sl.tokens == seen_tokens) continue;
+    seen_nb = sl.nb; seen_tokens = sl.tokens;
+    SsdArgs s;
+    chunk_args(a, sl.tokens, sl.nb, &s);
     pl.ws_bytes = std::max(pl.ws_bytes, align_up(ssd_b200_workspace_bytes(&s), 256));
   }
-  if (a->seqlen % pl.tokens != 0) {   // the shorter last chunk may be cut into segments differently
-    chunk_args(a, a->seqlen % pl.tokens, 1, &s);
-    pl.ws_bytes = std::max(pl.ws_bytes, align_up(ssd_b200_workspace_bytes(&s), 256));
-  }
-  pl.slot_bytes = 2 * pl.x_bytes + pl.ld_bytes + pl.ws_bytes;
+  // per-slice log-decay sums stay on the device until the end (one copy back)
+  pl.ldall_bytes = a->final_logdecay ? align_up((size_t)pl.nslices * k * a->nheads * 4, 256) : 0;
+  pl.slot_bytes = 2 * pl.x_bytes + pl.ws_bytes;
   // B, C, A, dt travel once per batch entry (small copies cost a fixed ~10 us each), double-buffered
   pl.entry_bytes = 2 * pl.bc_bytes + pl.a_bytes + pl.dt_bytes;
   // + the carried state (ping-pong), the entering state and the leaving state of a batch entry (two each)
-  pl.total_bytes = kSlots * pl.slot_bytes + 2 * pl.entry_bytes + 6 * pl.st_bytes + 256;
+  // + every slice's log-decay sums + the status word of the kernels
+  pl.total_bytes = kSlots * pl.slot_bytes + 2 * pl.entry_bytes + 6 * pl.st_bytes + pl.ldall_bytes + 256;
   return pl;
 }
 
@@ -126,43 +177,7 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
 
   const int e = esize(host->dtype);
   const int b = host->batch, s = host->seqlen, h = host->nheads, p = host->headdim, n = host->dstate, g = host->ngroups;
-  // The chunks of all batch entries in order.  The first entry opens and the last one closes with a ramp of smaller
-  // chunks (1/8, 1/8, 1/4, 1/2 of the regular length), so that the device->host stream starts early and the
-  // host->device stream ends late: the two directions then overlap for all but a fraction of a chunk.
-  struct Slice { int bi, nb, ci, t0, tokens; bool first, last; };   // nb batch entries from bi on
-  std::vector<Slice> slices;
-  {
-    int unit = host->chunk / gcd_int(host->chunk, 128) * 128;
-    if (s % unit != 0) unit = host->chunk;
-    for (int bi = 0; bi < b && pl.group > 1; bi += pl.group)
-      slices.push_back({bi, std::min(pl.group, b - bi), 0, 0, s, true, true});
-    for (int bi = 0; bi < b && pl.group == 1; ++bi) {
-      std::vector<int> lens;
-      int left = s;
-      const int ramp[4] = {pl.tokens / 8, pl.tokens / 8, pl.tokens / 4, pl.tokens / 2};
-      std::vector<int> head, tail;
-      if (bi == 0)
-        for (int k = 0; k < 4; ++k) {
-          const int len = ramp[k] / unit * unit;
-          if (len > 0 && left - len >= pl.tokens) { head.push_back(len); left -= len; }
-        }
-      if (bi == b - 1)
-        for (int k = 0; k < 4; ++k) {
-          const int len = ramp[k] / unit * unit;
-          if (len > 0 && left - len >= pl.tokens) { tail.insert(tail.begin(), len); left -= len; }
-        }
-      lens = head;
-      while (left > 0) { const int len = std::min(pl.tokens, left); lens.push_back(len); left -= len; }
-      // (ramp-down pieces are listed largest first, so that the last copies are the small ones)
-      std::sort(tail.begin(), tail.end(), [](int a, int c) { return a > c; });
-      lens.insert(lens.end(), tail.begin(), tail.end());
-      int t0 = 0;
-      for (size_t k = 0; k < lens.size(); ++k) {
-        slices.push_back({bi, 1, (int)k, t0, lens[k], k == 0, k + 1 == lens.size()});
-        t0 += lens[k];
-      }
-    }
-  }
+  const std::vector<Slice> slices = make_slices(host, pl.tokens, pl.group);
   const int nslices = (int)slices.size();
   // The per-entry buffers (B, C, A, dt, entering and leaving state) exist twice; `set` alternates per entry (group).
   int last_run_user[2] = {-1, -1};     // last slice whose kernels read buffer set 0 / 1
@@ -172,8 +187,6 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
 
   cudaStream_t st_in = nullptr, st_run = nullptr, st_out = nullptr;
   std::vector<cudaEvent_t> ev_in(nslices, nullptr), ev_run(nslices, nullptr), ev_out(nslices, nullptr);
-  std::vector<float> ld_host;   // per-chunk log-decay sums, added up on the host at the end
-  if (host->final_logdecay) ld_host.assign((size_t)nslices * pl.group * h, 0.f);
   int rc = SSD_OK;
   auto ck = [&](cudaError_t err) { if (err != cudaSuccess && rc == SSD_OK) rc = SSD_ERR_CUDA; };
   ck(cudaStreamCreateWithFlags(&st_in, cudaStreamNonBlocking));
@@ -191,6 +204,10 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
   float* carry[2] = {reinterpret_cast<float*>(st_base), reinterpret_cast<float*>(st_base + pl.st_bytes)};
   float* enter[2] = {reinterpret_cast<float*>(st_base + 2 * pl.st_bytes), reinterpret_cast<float*>(st_base + 3 * pl.st_bytes)};
   float* leave[2] = {reinterpret_cast<float*>(st_base + 4 * pl.st_bytes), reinterpret_cast<float*>(st_base + 5 * pl.st_bytes)};
+  float* ld_all = reinterpret_cast<float*>(st_base + 6 * pl.st_bytes);   // [slice][entry of the group][head]
+  int32_t* dev_status = reinterpret_cast<int32_t*>(st_base + 6 * pl.st_bytes + pl.ldall_bytes);
+  // every kernel of the pipeline reports a wait that ran out to this word (the kernels run on st_run, in order)
+  ck(cudaMemsetAsync(dev_status, 0, sizeof(int32_t), st_run));
   const char* hX = static_cast<const char*>(host->X);
   const char* hB = static_cast<const char*>(host->B);
   const char* hC = static_cast<const char*>(host->C);
@@ -206,8 +223,8 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
     char* slot = base + (size_t)(i % kSlots) * pl.slot_bytes;
     char* dX = slot;
     char* dY = dX + pl.x_bytes;
-    char* dL = dY + pl.x_bytes;
-    char* dW = dL + pl.ld_bytes;
+    char* dW = dY + pl.x_bytes;
+    float* dL = ld_all + (size_t)i * pl.group * h;
     char* eB = entry_base + (size_t)set * pl.entry_bytes;   // whole batch entries: B, C, A, dt
     char* eC = eB + pl.bc_bytes;
     char* eA = eC + pl.bc_bytes;
@@ -249,9 +266,10 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
     sa.Y = state_only ? nullptr : dY;
     sa.initial_state = first ? (host->initial_state ? enter[set] : nullptr) : carry[(ci - 1) & 1];
     sa.final_state = last ? (want_state ? leave[set] : nullptr) : carry[ci & 1];
-    sa.final_logdecay = host->final_logdecay ? reinterpret_cast<float*>(dL) : nullptr;
+    sa.final_logdecay = host->final_logdecay ? dL : nullptr;
     sa.workspace = pl.ws_bytes ? dW : nullptr;
     sa.workspace_bytes = pl.ws_bytes;
+    sa.status = dev_status;
     if (state_only && !sa.final_state) sa.final_state = carry[ci & 1];
     if (rc == SSD_OK) {
       const int frc = ssd_b200_forward(&sa, st_run);
@@ -268,16 +286,20 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
                          cudaMemcpyDeviceToHost, st_out));
       last_leave_user[set] = i;
     }
-    if (host->final_logdecay)
-      ck(cudaMemcpyAsync(ld_host.data() + (size_t)i * pl.group * h, dL, (size_t)nb * h * 4, cudaMemcpyDeviceToHost,
-                         st_out));
     ck(cudaEventRecord(ev_out[i], st_out));
   }
 
   if (st_in) ck(cudaStreamSynchronize(st_in));
   if (st_run) ck(cudaStreamSynchronize(st_run));
   if (st_out) ck(cudaStreamSynchronize(st_out));
+  int32_t dev_word = 0;
+  if (rc == SSD_OK) ck(cudaMemcpy(&dev_word, dev_status, sizeof(dev_word), cudaMemcpyDeviceToHost));
+  if (host->status) *host->status = dev_word;
+  if (rc == SSD_OK && dev_word != 0) rc = SSD_ERR_DEVICE_WAIT;
   if (host->final_logdecay && rc == SSD_OK) {
+    // per-slice sums, added up on the host
+    std::vector<float> ld_host((size_t)nslices * pl.group * h, 0.f);
+    ck(cudaMemcpy(ld_host.data(), ld_all, ld_host.size() * sizeof(float), cudaMemcpyDeviceToHost));
     std::vector<double> acc((size_t)b * h, 0.0);
     for (int i = 0; i < nslices; ++i)
       for (int eb = 0; eb < slices[i].nb; ++eb)

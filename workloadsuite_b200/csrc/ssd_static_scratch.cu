@@ -60,8 +60,9 @@ int ssd_b200_forward_static_scratch(const SsdArgs* args, void* stream) {
     a.workspace = scratch;
     a.workspace_bytes = kStaticScratchBytes;
   }
-  // Pass 1 of the segmented forward writes every segment state and log-decay sum
-  // it later reads, so nothing in the array has to start at zero.
+  // The two-pass forward writes every segment state and log-decay sum before it reads
+  // it; the single-launch (chained) forward needs its ready flags at zero and clears
+  // them itself with a memset on `stream`.  So the caller never has to clear the array.
   return ssd_b200_forward(&a, stream);
 }
 

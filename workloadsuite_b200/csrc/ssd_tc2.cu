@@ -74,7 +74,9 @@ struct Misc2 {
   uint64_t bar_yo, bar_s, bar_y[2];   // tcgen05.commit arrivals (the S and C.H MMAs serve both heads at once)
   uint64_t bar_xd, bar_h, bar_e;      // one arrival per compute warp of either head (8)
   uint64_t bar_p[2];                  // one arrival per compute warp of the head (4)
+  uint64_t bar_drain[3];              // give-up path: the MMAs of issuing warp 1 / 2 / 3 have all completed
   uint32_t tmem_base;
+  long long wait_clocks;     // bound of every wait (SM clock cycles)
   volatile int abort_flag;   // 0, or the status code of the first wait that gave up (every role then leaves)
   float wsum[2][4];
   // Double-buffered by tile parity: step c writes the next tile's values while step d still reads this tile's.
@@ -149,12 +151,22 @@ __device__ __forceinline__ bool wait2(uint64_t* bar, uint32_t parity, Misc2* m, 
   const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {   // (try_wait parks the thread for a short, hardware-chosen time by itself)
     if (m->abort_flag) return false;
-    if (clock64() - t0 > kWaitClocks) {
+    if (clock64() - t0 > m->wait_clocks) {
       m->abort_flag = code;   // reported to the caller's status word at kernel end
       return false;
     }
   }
   return true;
+}
+
+// Last act of an MMA-issuing thread: tensor memory is freed at the end of the kernel, so the MMAs this thread
+// has issued must have completed by then -- also when the roles that would have waited for them gave up
+// (bounded, like every wait).
+__device__ __forceinline__ void drain_mmas(Misc2* m, int which) {
+  umma_commit(&m->bar_drain[which]);
+  const long long t0 = clock64();
+  while (!mbar_try_wait(&m->bar_drain[which], 0))
+    if (clock64() - t0 > m->wait_clocks) break;
 }
 
 #ifdef SSD_TC2_TRACE
@@ -193,6 +205,9 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     if (threadIdx.x == 0 && sp.status) atomicCAS(sp.status, 0, (int)STATUS_BAD_SMEM_ALIGNMENT);
     return;
   }
+  // (fault injection for the tests of the give-up path: the first CTA of a chained launch never publishes its
+  //  hand-over, so the CTA that continues its sequence runs into the bound of its wait)
+  if (sp.inject_lost_handover && sp.chain && blockIdx.x == 0) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool want_y = sp.compute_y != 0;
   int32_t* status = sp.status;
@@ -218,7 +233,9 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       mbar_init(&m->bar_y[h], 1);
       mbar_init(&m->bar_p[h], 4);   // one arrival per compute warp (lane 0, after a warp barrier)
     }
+    for (int i = 0; i < 3; ++i) mbar_init(&m->bar_drain[i], 1);
     m->abort_flag = 0;
+    m->wait_clocks = sp.wait_clocks;
     work_list(prm, &m->work);
     fence_mbar_init();
   }
@@ -311,6 +328,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           umma_commit(&m->empty_b);
         }
       }
+      drain_mmas(m, 0);
     } else if (warp == 2 && lane == 0) {
       // ---------------------------------------------------------------- MMA issuer for S = B^T.[Xd0|Xd1] and Y = C.[H0|H1]
       // The two heads' Xd (and state copies) lie one 64-column block apart in shared memory, so one
@@ -361,6 +379,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         }
         k0 += nt;
       }
+      drain_mmas(m, 1);
     } else if (warp == 3 && lane == 0) {
       // ---------------------------------------------------------------- MMA issuer for Y_h += P_h . X_h, head 0 then head 1
       if (want_y) {
@@ -390,6 +409,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           }
         }
       }
+      drain_mmas(m, 2);
     }
   } else {
     // ------------------------------------------------------------------ compute warpgroups (warps 4-7: head 0, 8-11: head 1)
@@ -758,7 +778,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(f) : "l"(sp.chain_flag + slot) : "memory");
                 if (f >= 4) break;   // all four warps of the predecessor's warpgroup have published
                 if (m->abort_flag) break;
-                if (clock64() - c0 > kWaitClocks) {
+                if (clock64() - c0 > m->wait_clocks) {
                   m->abort_flag = (int)STATUS_WAIT_TIMEOUT_CHAIN;
                   break;
                 }

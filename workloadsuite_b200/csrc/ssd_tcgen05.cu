@@ -51,6 +51,7 @@ struct Misc {
   uint64_t full_b, full_c, full_x[2], empty_b, empty_c, empty_x[2];
   uint64_t bar_g, bar_xd, bar_s, bar_p, bar_y, bar_h, bar_e[2];
   uint32_t tmem_base;
+  long long wait_clocks;   // bound of every wait (SM clock cycles)
   volatile int abort_flag;
   float wsum[2][4];
   alignas(16) float cs2[2][T];   // prefix sums times log2(e), double-buffered by tile parity
@@ -69,7 +70,7 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Mi
     if (mbar_try_wait(bar, parity)) return true;
     if ((++it & 63) == 0) {
       if (m->abort_flag) return false;
-      if (clock64() - t0 > kWaitClocks) {
+      if (clock64() - t0 > m->wait_clocks) {
         m->abort_flag = 1;
         if (status) atomicCAS(status, 0, code);
         return false;
@@ -107,6 +108,7 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     mbar_init(&m->bar_xd, 128); mbar_init(&m->bar_p, 128); mbar_init(&m->bar_h, 128);
     mbar_init(&m->bar_e[0], 128); mbar_init(&m->bar_e[1], 128);
     m->abort_flag = 0;
+    m->wait_clocks = prm.sp.wait_clocks;
     fence_mbar_init();
   }
   if (warp == 0) tmem_alloc(&m->tmem_base, 512);

@@ -19,7 +19,6 @@ constexpr int T = 128;          // tokens per tile
 constexpr int P = 64;           // head dim
 constexpr int kBlk = T * 128;   // bytes of one [128 rows x 64 cols] 16-bit swizzled block
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr long long kWaitClocks = 2000000000LL;  // about one second
 
 template <typename T16>
 __device__ __forceinline__ float2 unpack2(uint32_t v);

@@ -74,10 +74,11 @@ class SequenceShardedSSD:
     Rank r holds tokens ``[r*s/R, (r+1)*s/R)`` of every tensor.  ``forward`` returns
     the local Y shard.  Buffers for the exchange are allocated once per shape.
 
-    With ``cuda_graphs=True`` the two local phases (everything before and everything after
-    the all-gather) are captured into CUDA graphs the first time a given set of tensors is
-    seen and replayed afterwards; the collective itself is always launched normally.  The
-    returned Y is then the same tensor on every call with those inputs.
+    With ``cuda_graphs=True`` the whole step (local scan, all-gather, fold, seeded scan) is
+    captured into one CUDA graph the first time a given set of tensors is seen and replayed
+    afterwards; if the collective cannot be captured, the two local phases are captured and the
+    collective is launched normally between them.  The returned Y is then the same tensor on
+    every call with those inputs.
     """
 
     def __init__(self, group: Optional[dist.ProcessGroup] = None, scan_fn: Callable = _cuda_scan,
@@ -91,6 +92,8 @@ class SequenceShardedSSD:
         self._send = None
         self._recv = None
         self._graphs = {}
+        self._one_graph = None      # None: not tried yet; True/False: the collective is / is not inside the graph
+        self._last = None
 
     def _buffers(self, numel: int, device):
         if self._send is None or self._send.numel() != numel or self._send.device != device:
@@ -120,12 +123,16 @@ class SequenceShardedSSD:
         h_in = initial_states if self.rank == 0 else self.fold_fn(states, lds, self.rank, initial_states)
         return self.scan_fn(X, A, B, C, chunk, dt=dt, initial_states=h_in, state_only=False, **kw)
 
+    def _exchange(self):
+        # phase 2: the only collective -- every rank's (state, log-decay) lands in every rank's own memory
+        dist.all_gather_into_tensor(self._recv, self._send, group=self.group)
+
     def forward(self, X, A, B, C, chunk, dt=None, initial_states=None, **kw):
+        self._last = (X, A, B, C, chunk, dt, initial_states, dict(kw))
         if self.cuda_graphs and X.is_cuda:
             return self._forward_graphed(X, A, B, C, chunk, dt, initial_states, kw)
         dims = self._phase_local(X, A, B, C, chunk, dt, kw)
-        # phase 2: the only collective -- every rank's (state, log-decay) to every rank
-        dist.all_gather_into_tensor(self._recv, self._send, group=self.group)
+        self._exchange()
         return self._phase_seeded(X, A, B, C, chunk, dt, initial_states, dims, kw)
 
     def _forward_graphed(self, X, A, B, C, chunk, dt, initial_states, kw):
@@ -135,26 +142,92 @@ class SequenceShardedSSD:
                None if out is None else out.data_ptr(), tuple(sorted((k, str(v)) for k, v in kw.items() if k != "out")))
         entry = self._graphs.get(key)
         if entry is None:
-            # one ordinary run first: allocates workspaces and exchange buffers outside any capture
+            # one ordinary run first: allocates workspaces and exchange buffers and warms the communicator
+            # outside any capture
             dims = self._phase_local(X, A, B, C, chunk, dt, kw)
-            dist.all_gather_into_tensor(self._recv, self._send, group=self.group)
+            self._exchange()
             self._phase_seeded(X, A, B, C, chunk, dt, initial_states, dims, kw)
             torch.cuda.synchronize(X.device)
             cap = torch.cuda.Stream(device=X.device)
-            g1, g2 = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
-            with torch.cuda.stream(cap):
-                with torch.cuda.graph(g1, stream=cap):
-                    dims = self._phase_local(X, A, B, C, chunk, dt, kw)
-                with torch.cuda.graph(g2, stream=cap):
-                    Y = self._phase_seeded(X, A, B, C, chunk, dt, initial_states, dims, kw)
-            torch.cuda.synchronize(X.device)
-            entry = (g1, g2, Y)
+            entry = None
+            if self._one_graph is not False:
+                # the whole step -- local scan, all-gather, fold, seeded scan -- as ONE graph: a step is one replay
+                try:
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.stream(cap):
+                        with torch.cuda.graph(g, stream=cap):
+                            dims = self._phase_local(X, A, B, C, chunk, dt, kw)
+                            self._exchange()
+                            Y = self._phase_seeded(X, A, B, C, chunk, dt, initial_states, dims, kw)
+                    torch.cuda.synchronize(X.device)
+                    entry = ((g,), Y)
+                    self._one_graph = True
+                except Exception:          # the collective could not be captured: keep it outside the graphs
+                    self._one_graph = False
+                    torch.cuda.synchronize(X.device)
+            if entry is None:
+                g1, g2 = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+                with torch.cuda.stream(cap):
+                    with torch.cuda.graph(g1, stream=cap):
+                        dims = self._phase_local(X, A, B, C, chunk, dt, kw)
+                    with torch.cuda.graph(g2, stream=cap):
+                        Y = self._phase_seeded(X, A, B, C, chunk, dt, initial_states, dims, kw)
+                torch.cuda.synchronize(X.device)
+                entry = ((g1, g2), Y)
             self._graphs[key] = entry
-        g1, g2, Y = entry
-        g1.replay()
-        dist.all_gather_into_tensor(self._recv, self._send, group=self.group)
-        g2.replay()
+        graphs, Y = entry
+        if len(graphs) == 1:
+            graphs[0].replay()
+        else:
+            graphs[0].replay()
+            self._exchange()
+            graphs[1].replay()
         return Y
+
+    # ---- accounting for the benchmark -------------------------------------------------------------------
+    def launch_mode(self) -> str:
+        if not self.cuda_graphs:
+            return "eager"
+        if self._one_graph:
+            return "cuda_graph (local scan + all-gather + fold + seeded scan in one graph)"
+        if self._one_graph is False:
+            return "cuda_graph (local phases) + eager all-gather"
+        return "cuda_graph"
+
+    def launches_per_step(self, X, A, B, C, chunk, **kw) -> int:
+        """Kernels of this library per step and rank (the collective's own kernel and the two small copies
+        into the send buffer are not counted)."""
+        from .ssd import plan
+
+        kw = {k: v for k, v in kw.items() if k in ("kernel", "nsegments")}
+        p_state = plan(X, A, B, C, chunk, state_only=True, **kw)
+        p_full = plan(X, A, B, C, chunk, **kw)
+        seeded = p_full["launches"] - 1 if p_full["nsegments"] > 1 and p_full["launches"] == 3 else p_full["launches"]
+        fold = 1 if self.rank > 0 else 0
+        return p_state["launches"] + fold + seeded
+
+    def phase_times_ms(self, repeats: int = 10):
+        """CUDA-event times of the phases of the last ``forward`` (eager launches on the current stream, median over
+        ``repeats``, this rank): local state-only scan, exchange, fold + seeded scan.  Collective on every rank."""
+        if getattr(self, "_last", None) is None:
+            return None
+        X, A, B, C, chunk, dt, initial_states, kw = self._last
+        if not X.is_cuda:
+            return None
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(repeats)]
+        for r in range(repeats):
+            dist.barrier(group=self.group)
+            ev[r][0].record()
+            dims = self._phase_local(X, A, B, C, chunk, dt, kw)
+            ev[r][1].record()
+            self._exchange()
+            ev[r][2].record()
+            self._phase_seeded(X, A, B, C, chunk, dt, initial_states, dims, kw)
+            ev[r][3].record()
+        torch.cuda.synchronize(X.device)
+        med = lambda i: sorted(e[i].elapsed_time(e[i + 1]) for e in ev)[repeats // 2]
+        return {"local_state_scan": med(0), "all_gather": med(1), "fold_and_seeded_scan": med(2),
+                "note": "eager launches with events between the phases (the timed step replays one graph)"}
 
 
 def sequence_sharded_forward(X, A, B, C, chunk, group=None, dt=None, initial_states=None, **kw):

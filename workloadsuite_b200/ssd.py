@@ -32,7 +32,8 @@ def _status_word(device) -> torch.Tensor:
 
 def device_status(device="cuda:0", clear: bool = True) -> int:
     """Synchronises and returns the kernels' status word for ``device`` (0 = fine; 1/2/3 = a bounded
-    wait on TMA / tensor-core / intra-CTA synchronisation ran out and the kernel gave up)."""
+    wait on TMA / tensor-core / intra-CTA synchronisation ran out and the kernel gave up; 6 = the wait for
+    the piece of a sequence handed over by another CTA ran out)."""
     device = torch.device(device)
     st = _status_word(device)
     torch.cuda.synchronize(device)
@@ -71,9 +72,35 @@ def _strides3(t: torch.Tensor, name: str):
     return (C.c_int64 * 3)(*st)
 
 
+def _same_device(ref: torch.Tensor, **tensors):
+    """Every tensor handed to the library must live where X lives: a pointer into host memory or into another
+    GPU's memory would fault inside a kernel instead of raising here."""
+    for name, t in tensors.items():
+        if t is not None and t.device != ref.device:
+            raise ValueError(f"{name} is on {t.device}, X is on {ref.device}: all tensors must share one device")
+
+
+def _rows_contiguous(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    """The kernels read rows of p (or n) contiguous elements.  A tensor whose innermost axis is strided -- the
+    reference block hands ``_ssd_core`` an X that is sequence-contiguous and channel-strided, a permuted
+    ``[b, d, l]`` buffer (``model_ref.py:83-89``) -- is copied once into the row layout (one read and one
+    write of the tensor); anything else is passed through as the view it is."""
+    if t is None or t.stride(-1) == 1 or t.shape[-1] == 1:
+        return t
+    return t.contiguous()
+
+
+def _check_out(out: torch.Tensor, like: torch.Tensor, name: str = "out"):
+    if out.shape != like.shape or out.dtype != like.dtype or out.device != like.device:
+        raise ValueError(f"{name} must have the shape {tuple(like.shape)}, dtype {like.dtype} and device of X")
+    if out.dim() and out.stride(-1) != 1 and out.shape[-1] != 1:
+        raise ValueError(f"{name}: innermost axis must be contiguous")
+
+
 def _check(X, A, B, Cm, dt, initial_states):
     if X.dim() != 4 or A.dim() != 3 or B.dim() != 4 or Cm.dim() != 4:
         raise ValueError("expected X[b,s,h,p], A[b,s,h], B[b,s,g,n], C[b,s,g,n]")
+    _same_device(X, A=A, B=B, C=Cm, dt=dt, initial_states=initial_states)
     b, s, h, p = X.shape
     g, n = B.shape[2], B.shape[3]
     if A.shape != (b, s, h) or B.shape[:2] != (b, s) or Cm.shape != B.shape:
@@ -147,6 +174,8 @@ def ssd_forward(
     D: Optional[torch.Tensor] = None,
     z: Optional[torch.Tensor] = None,
     separate_epilogue: bool = False,
+    wait_limit_ms: int = 0,
+    inject_lost_handover: bool = False,
 ):
     """Mamba-2 SSD forward ``Y = SSD(X, A, B, C)`` on the current CUDA stream.
 
@@ -157,7 +186,14 @@ def ssd_forward(
     the carry at ``model_ref.py:153``) or None for zeros.  ``chunk`` is the
     reference's ``block_len``: it must divide ``s`` (as at ``model_ref.py:106``);
     the result does not otherwise depend on it.  Views with a contiguous innermost
-    axis are accepted as they are.  No host synchronisation.
+    axis are accepted as they are; a tensor whose innermost axis is strided (the
+    reference block's own X, ``model_ref.py:83-89``) is first copied into the row layout.
+    All tensors must be on X's device.  No host synchronisation.
+
+    A sequence that is cut into segments uses one scratch buffer per device, kept between
+    calls and shared by all of them: calls that may overlap on the GPU (different streams)
+    must be serialised by the caller, and ``reuse_segments`` relies on no other segmented
+    call on that device coming between the two runs.
 
     ``D`` [h] and ``z`` [b,s,h,p] (dtype of X) add the layer's skip and gate to the kernel's epilogue:
     ``Y <- (Y + X * D[head]) * silu(z)`` (``model_ref.py:116-118``), evaluated in float32 and rounded once;
@@ -168,22 +204,31 @@ def ssd_forward(
     the summed log-decay [b,h] when asked.  With ``state_only`` no Y is produced.
     ``reuse_segments`` tells a segmented two-pass scan that the previous call on this device was the
     ``state_only`` run over the same tensors, so its per-segment states need not be recomputed.
+
+    Every wait inside the kernels is bounded (about a second; ``wait_limit_ms`` sets another bound): a kernel
+    that runs into the bound writes a code to the device status word (``device_status``) and returns.
+    ``inject_lost_handover`` exists to test that path: see ``SSD_FLAG_INJECT_LOST_HANDOVER``.
     """
     if not X.is_cuda:
         raise RuntimeError("ssd_forward needs CUDA tensors (there is no CPU path); see ssd_forward_host")
     b, s, h, p, g, n = _check(X, A, B, C_, dt, initial_states)
     if h % g != 0:
         raise ValueError("n_heads must be divisible by n_groups")
+    X, B, C_, z = _rows_contiguous(X), _rows_contiguous(B), _rows_contiguous(C_), _rows_contiguous(z)
     if initial_states is not None:
         initial_states = initial_states.contiguous()
     if D is not None:
         if D.shape != (h,):
             raise ValueError("D must be [h]")
         D = D.to(device=X.device, dtype=torch.float32).contiguous()
-    if z is not None and (z.shape != X.shape or z.dtype != X.dtype or not z.is_cuda):
-        raise ValueError("z must be a CUDA tensor [b,s,h,p] in the dtype of X")
+    if z is not None and (z.shape != X.shape or z.dtype != X.dtype or z.device != X.device):
+        raise ValueError("z must be a tensor [b,s,h,p] in the dtype and on the device of X")
     if state_only and (D is not None or z is not None):
         raise ValueError("D / z apply to Y; a state-only run produces none")
+    if out is not None:
+        if state_only:
+            raise ValueError("a state-only run writes no Y: do not pass out")
+        _check_out(out, X)
     lib = _lib.load()
     dev = X.device
     want_final = return_final_state or state_only
@@ -197,6 +242,9 @@ def ssd_forward(
           reuse_segments)
     if separate_epilogue:
         args.flags |= _lib.FLAG_SEPARATE_EPILOGUE
+    if inject_lost_handover:
+        args.flags |= _lib.FLAG_INJECT_LOST_HANDOVER
+    args.wait_limit_ms = int(wait_limit_ms)
     if D is not None:
         args.D = D.data_ptr()
     if z is not None:
@@ -232,14 +280,17 @@ def conv1d_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     if x.dim() != 3 or x.stride(2) != 1 or x.dtype not in _DTYPES:
         raise ValueError("x must be [b,l,d] float32/float16/bfloat16 with a contiguous channel axis")
     b, l, d = x.shape
+    _same_device(x, weight=weight, bias=bias, out=out)
     w = weight.reshape(d, -1).to(x.dtype).contiguous()
     taps = w.shape[1]
     if bias is not None:
+        if bias.shape != (d,):
+            raise ValueError("bias must be [d]")
         bias = bias.to(x.dtype).contiguous()
     if out is None:
         out = torch.empty((b, l, d), dtype=x.dtype, device=x.device)
-    elif out.shape != x.shape or out.dtype != x.dtype or out.stride(2) != 1:
-        raise ValueError("out must be [b,l,d] in the dtype of x with a contiguous channel axis")
+    else:
+        _check_out(out, x)
     lib = _lib.load()
     with torch.cuda.device(x.device):
         rc = lib.ssd_b200_conv1d_silu(x.data_ptr(), w.data_ptr(), bias.data_ptr() if bias is not None else None,
@@ -260,9 +311,12 @@ def dt_prologue(dt_raw: torch.Tensor, dt_bias: Optional[torch.Tensor], A_log: to
     if dt_raw.dim() != 3 or dt_raw.stride(2) != 1 or dt_raw.dtype not in _DTYPES:
         raise ValueError("dt_raw must be [b,l,h] float32/float16/bfloat16 with a contiguous head axis")
     b, l, h = dt_raw.shape
+    _same_device(dt_raw, dt_bias=dt_bias, A_log=A_log)
+    if A_log.shape != (h,) or (dt_bias is not None and dt_bias.shape != (h,)):
+        raise ValueError("dt_bias and A_log must be [h]")
     if dt_bias is not None:
         dt_bias = dt_bias.to(dt_raw.dtype).contiguous()
-    A_log = A_log.to(device=dt_raw.device, dtype=torch.float32).contiguous()
+    A_log = A_log.to(dtype=torch.float32).contiguous()
     dt = torch.empty((b, l, h), dtype=dt_raw.dtype, device=dt_raw.device)
     A_dt = torch.empty((b, l, h), dtype=torch.float32, device=dt_raw.device)
     lib = _lib.load()
@@ -306,12 +360,19 @@ def fold_states(states: torch.Tensor, logdecays: torch.Tensor, rank: int,
     logdecays float32 [R,b,h]; both may be strided along R (slices of one
     all-gather buffer).  ``H_in(r+1) = exp(D_r) H_in(r) + F_r``.
     """
+    if not states.is_cuda:
+        raise RuntimeError("fold_states needs CUDA tensors (there is no CPU path)")
     R, b, h, n, p = states.shape
+    _same_device(states, logdecays=logdecays, initial=initial)
+    if logdecays.shape != (R, b, h) or (initial is not None and initial.shape != (b, h, n, p)):
+        raise ValueError("expected states [R,b,h,n,p], logdecays [R,b,h], initial [b,h,n,p]")
     if not states[0].is_contiguous() or not logdecays[0].is_contiguous():
         states, logdecays = states.contiguous(), logdecays.contiguous()
     if states.dtype != torch.float32 or logdecays.dtype != torch.float32:
         raise TypeError("states and logdecays must be float32")
     if initial is not None:
+        if initial.dtype != torch.float32:
+            raise TypeError("initial must be float32")
         initial = initial.contiguous()
     out = torch.empty((b, h, n, p), dtype=torch.float32, device=states.device)
     lib = _lib.load()
