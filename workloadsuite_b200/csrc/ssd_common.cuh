@@ -95,4 +95,5 @@ int tc2_default_segments(const SsdArgs& a);
 bool tc2_chain_segments(const SsdArgs& a, int nseg);   // true: one chained pass; false: two passes + fold
 int launch_tc2(const SsdArgs& a, const ScanParams& prm, cudaStream_t stream);
 
+
 }  // namespace ssd

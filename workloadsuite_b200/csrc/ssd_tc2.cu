@@ -151,7 +151,9 @@ __device__ __forceinline__ bool wait2(uint64_t* bar, uint32_t parity, Misc2* m, 
   const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {   // (try_wait parks the thread for a short, hardware-chosen time by itself)
     if (m->abort_flag) return false;
-    if (clock64() - t0 > m->wait_clocks) {
+    // (twice the bound of the wait for another CTA's hand-over: everything inside the CTA may be waiting behind
+    //  that one, and the wait that is the cause should be the one that reports)
+    if (clock64() - t0 > 2 * m->wait_clocks) {
       m->abort_flag = code;   // reported to the caller's status word at kernel end
       return false;
     }
