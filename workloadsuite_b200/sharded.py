@@ -56,6 +56,7 @@ def _cuda_scan(X, A, B, C, chunk, dt=None, initial_states=None, state_only=False
     from .ssd import ssd_forward
 
     if state_only:
+        kw = {k: v for k, v in kw.items() if k != "out"}      # (the state-only phase writes no Y)
         return ssd_forward(X, A, B, C, chunk, dt=dt, initial_states=initial_states, state_only=True,
                            return_logdecay=True, **kw)
     # the state-only call that precedes this one left its per-segment states in the workspace
