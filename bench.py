@@ -442,11 +442,12 @@ def build_step(W, sharded, cfg, rank, world, dev, kw, no_graphs, seq_parallel):
     return sets, outs, run_step, info
 
 
-def model_through_reference_harness(dev, steps):
+def model_through_reference_harness(dev, steps, with_compile=True):
     """The drop-in ``Model`` and the reference ``Model`` (``model_ref.py:165-229``, production configuration: 24
     layers, b8 s2048 d_model 2048, fp16) timed on this GPU by the reference's own ``_benchmark``
     (``bench.py:138-170``) under ``torch.inference_mode()`` as ``_bench_workload`` does (``bench.py:230-233``), with
-    shared weights, plus the output parity of the two on sampled rows."""
+    shared weights, plus the output parity of the two on sampled rows; and the reference under ``torch.compile``
+    through the reference's ``_compile_and_bench`` (about a minute of compilation)."""
     from oracle import build_ref as R
     from workloadsuite_b200 import mamba_model as MM
 
@@ -479,11 +480,19 @@ def model_through_reference_harness(dev, steps):
     with torch.inference_mode():
         out["reference_eager"] = rb._benchmark(ref, [x], **common)
         yr = ref(x)
+        if with_compile:
+            # the reference harness's second variant: the very instance it timed, under torch.compile
+            # (bench.py:172-201, 241-253; mode "default", dynamic False, fullgraph False)
+            out["reference_torch_compile"] = rb._compile_and_bench(ref, [x], compile_mode="default", dynamic=False,
+                                                                   **common)
     rows = torch.linspace(0, MM.seq_length - 1, 64, device=dev).long()
     a, b_ = yo[:, rows].double(), yr[:, rows].double()
     out["parity_sampled_rows"] = {"max_abs_err_over_max_abs_ref": float((a - b_).abs().max() / b_.abs().max()),
                                   "tol": 2e-2, "finite": bool(torch.isfinite(yo).all())}
     out["speedup_vs_reference_eager"] = out["reference_eager"]["median_ms"] / out["dropin"]["median_ms"]
+    if "median_ms" in out.get("reference_torch_compile", {}):
+        out["speedup_vs_reference_torch_compile"] = (out["reference_torch_compile"]["median_ms"] /
+                                                     out["dropin"]["median_ms"])
     out["tokens_per_s"] = MM.batch_size * MM.seq_length / (out["dropin"]["median_ms"] * 1e-3)
     del ref, ours
     torch.cuda.empty_cache()
@@ -503,6 +512,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-others", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the parity leg (profiling runs only)")
+    ap.add_argument("--no-model-compile", action="store_true",
+                    help="skip the torch.compile variant of the reference Model (about a minute of compilation)")
     ap.add_argument("--min-seconds", type=float, default=MIN_TIMED_SECONDS,
                     help="repeat the --steps block until this much GPU time has been measured")
     ap.add_argument("--no-graphs", action="store_true",
@@ -555,7 +566,10 @@ def main():
     ms_step, t0, t1, blocks = time_blocks(run_step, nsets, args.steps, args.warmup, dist_on, args.min_seconds)
     sampler.stop()
     clocks = sampler.summary(t0, t1)
-    phases = info["engine"].phase_times_ms() if "engine" in info else None
+    phases = None
+    if "engine" in info:     # (how the step was launched is known once it has run)
+        info["launch_mode"] = info["engine"].launch_mode()
+        phases = info["engine"].phase_times_ms()
 
     tokens = cfg["b"] * cfg["s"]
     value = tokens / (ms_step * 1e-3)
@@ -609,7 +623,7 @@ def main():
             ms3, _, _, blocks3 = time_blocks(step3, info3["nsets"], max(5, args.steps // 2), 3, dist_on, args.min_seconds)
             others[key] = {"tokens_per_s": c3["b"] * c3["s"] / (ms3 * 1e-3), "ms_per_step": ms3, "blocks": len(blocks3),
                            "hbm_frac_of_measured": info3["set_bytes"] / (ms3 * 1e-3) / 1e9 / peak,
-                           "launch": info3["launch_mode"], "kernel_launches_per_step": info3["launches"],
+                           "launch": info3["engine"].launch_mode(), "kernel_launches_per_step": info3["launches"],
                            "segments_per_sequence": info3["plan"]["nsegments"], "parity": p3,
                            "phases_ms": info3["engine"].phase_times_ms()}
             del s3, o3, step3, info3
@@ -660,11 +674,18 @@ def main():
                 Y = Y + d["X"] * Dv.to(Y.dtype).view(1, 1, -1, 1)
                 Y = Y * torch.nn.functional.silu(zz[i])
 
+            def st_separate(i):
+                d = ss[i]
+                W.ssd_forward(d["X"], d["A"], d["B"], d["C"], c["chunk"], initial_states=d.get("initial_states"),
+                              out=oo[i], kernel=args.kernel, D=Dv, z=zz[i], separate_epilogue=True)
+
             ms_f, _, _, _ = time_blocks(st_fused, ns, max(5, args.steps // 2), 3, False, args.min_seconds / 2)
+            ms_s, _, _, _ = time_blocks(st_separate, ns, max(5, args.steps // 2), 3, False, args.min_seconds / 4)
             ms_u, _, _, _ = time_blocks(st_unfused, ns, max(5, args.steps // 2), 3, False, args.min_seconds / 4)
             others[args.workload + "+skip_gate"] = {
                 "tokens_per_s": c["b"] * c["s"] / (ms_f * 1e-3), "ms_per_step": ms_f,
                 "hbm_frac_of_measured": sb / (ms_f * 1e-3) / 1e9 / peak,
+                "ms_per_step_with_standalone_epilogue_kernel": ms_s,
                 "ms_per_step_with_pytorch_epilogue": ms_u}
             del ss, oo, zz
             torch.cuda.empty_cache()
@@ -697,7 +718,8 @@ def main():
         # The whole Model (reference contract: Model / get_init_inputs / get_inputs, model_ref.py:165-229) at the
         # reference's production configuration, drop-in next to the reference, timed by the reference's harness.
         try:
-            others["mamba_model_24_layers"] = model_through_reference_harness(dev, args.steps)
+            others["mamba_model_24_layers"] = model_through_reference_harness(dev, args.steps,
+                                                                              with_compile=not args.no_model_compile)
         except Exception as exc:
             others["mamba_model_24_layers"] = {"error": f"{type(exc).__name__}: {exc}"}
             torch.cuda.empty_cache()

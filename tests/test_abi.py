@@ -154,13 +154,25 @@ def test_plan_of_the_benchmark_configurations(lib):
     k, nseg, launches = _plan(lib, _shape(4, 8192, 80, 64, 128, 1, 256, _lib.DTYPE_BF16))
     assert (k, launches) == (TC, 1) and nseg == 2
     assert lib.ssd_b200_workspace_bytes(C.byref(_shape(4, 8192, 80, 64, 128, 1, 256, _lib.DTYPE_BF16))) > 0
-    # its head shards at 2 and 8 GPUs: one pass with a CTA per pair; two passes and a fold
-    assert _plan(lib, _shape(4, 8192, 40, 64, 128, 1, 256, _lib.DTYPE_BF16)) == (TC, 1, 1)
-    k, nseg, launches = _plan(lib, _shape(4, 8192, 10, 64, 128, 1, 256, _lib.DTYPE_BF16))
-    assert k == TC and nseg > 1 and launches == 3
-    # config 3 (one long sequence, 16 pairs): two passes; config 4 (6144 short sequences): whole sequences, one launch
+    # its head shards at 2 and 8 GPUs (80 and 20 head pairs for 148 SMs): the same even deal in one launch, each CTA
+    # first scanning the last piece of its range from zero so that the pieces after it need not wait ("look-back")
+    for heads in (40, 10):
+        k, nseg, launches = _plan(lib, _shape(4, 8192, heads, 64, 128, 1, 256, _lib.DTYPE_BF16))
+        assert k == TC and nseg > 1 and launches == 1
+    # config 3 (one long sequence, 16 pairs): look-back too; its state-only run and the run that reuses the segment
+    # states (the two halves of a sequence-sharded forward) stay two passes and a fold
     k, nseg, launches = _plan(lib, _shape(1, 131072, 32, 64, 128, 1, 256, _lib.DTYPE_BF16))
-    assert k == TC and nseg > 4 and launches == 3
+    assert k == TC and nseg > 1 and launches == 1
+    so = _shape(1, 131072, 32, 64, 128, 1, 256, _lib.DTYPE_BF16)
+    so.flags = _lib.FLAG_STATE_ONLY
+    k, nseg, launches = _plan(lib, so)
+    assert k == TC and nseg > 4 and launches == 2
+    so.flags = _lib.FLAG_REUSE_SEGMENTS
+    assert _plan(lib, so) == (TC, nseg, 2)
+    # 96 pairs of only 16 tiles (config 1): the state-only scans and the start-ups would eat the gain: whole sequences
+    assert _plan(lib, _shape(8, 2048, 24, 64, 128, 1, 256, _lib.DTYPE_BF16))[1:] == (1, 1)
+    assert _plan(lib, _shape(8, 8192, 24, 64, 128, 1, 256, _lib.DTYPE_BF16))[1:] == (2, 1)
+    # config 4 (6144 short sequences): whole sequences, one launch
     assert _plan(lib, _shape(256, 512, 48, 64, 64, 8, 128, _lib.DTYPE_BF16)) == (TC, 1, 1)
     # config 0 is fp32: the CUDA-core recurrence
     assert _plan(lib, _shape(16, 128, 8, 64, 16, 8, 64, _lib.DTYPE_F32))[0] == SCAN

@@ -252,7 +252,11 @@ def test_reuse_of_segment_states_after_a_state_only_run():
         W.ssd_forward(d["X"], d["A"], d["B"], d["C"], 256, state_only=True, kernel=kernel, nsegments=4)
         got = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], 256, initial_states=d["initial_states"], kernel=kernel,
                             nsegments=4, reuse_segments=True)
-        assert torch.equal(got, want)
+        # (the plain tensor-core run joins its pieces in another order of operations: look-back in one launch)
+        assert max(O.error_metrics(got.cpu(), want.cpu())) < 5e-3
+        again = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], 256, initial_states=d["initial_states"], kernel=kernel,
+                              nsegments=4, reuse_segments=True)
+        assert torch.equal(got, again)
 
 
 def test_state_only_and_logdecay_outputs():
@@ -352,21 +356,27 @@ def _check_sampled_units(Y, inp, units, H=None, tol=2e-2):
 
 @pytest.mark.parametrize("decay_scale", [1.0, 0.02])
 def test_full_size_config3_long_sequence(decay_scale):
-    """Config 3 at its stated size (one sequence of 131 072 tokens, 32 heads: 1 024 tiles per sequence, cut into
-    segments by the default plan): first, last and two middle heads against the float64 recurrence over all tokens,
-    with the configuration's own decays and with slow decays (so that what crosses the segment cuts matters), plus
-    the final state."""
+    """Config 3 at its stated size (one sequence of 131 072 tokens, 32 heads: 16 head pairs of 1 024 tiles, dealt out
+    over 148 CTAs in pieces of 110-111 tiles that fold up to nine predecessors): first, last and two middle heads
+    against the float64 recurrence over all tokens, with the configuration's own decays and with slow decays (so
+    that what crosses the cuts matters), plus the final state; and the two-pass path (state-only run, then the run
+    that reuses its segment states) against the same."""
     W = _ssd()
     cfg, inp = _full("cfg3", seed=3)
     if decay_scale != 1.0:
         inp["A"] = inp["A"] * decay_scale
     d = _to_dev(inp)
     plan = W.plan(d["X"], d["A"], d["B"], d["C"], cfg["chunk"])
-    assert plan["nsegments"] >= 9 and plan["kernel"] == "tcgen05"
+    assert plan["nsegments"] > 1 and plan["launches"] == 1 and plan["kernel"] == "tcgen05"     # look-back, 148 pieces
     Y, H = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], cfg["chunk"], return_final_state=True)
     torch.cuda.synchronize()
     assert torch.isfinite(Y).all() and torch.isfinite(H).all()
     _check_sampled_units(Y, inp, [(0, 0), (0, 13), (0, 18), (0, cfg["h"] - 1)], H=H)
+    if decay_scale != 1.0:
+        H2 = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], cfg["chunk"], state_only=True)
+        Y2 = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], cfg["chunk"], reuse_segments=True)
+        torch.cuda.synchronize()
+        _check_sampled_units(Y2, inp, [(0, 0), (0, cfg["h"] - 1)], H=H2)
 
 
 def test_full_size_config4_many_short_sequences_with_initial_states():

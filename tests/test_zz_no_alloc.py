@@ -61,16 +61,18 @@ def test_static_scratch_entry_matches_workspace_entry_twice():
             assert O.error_metrics(got.cpu(), Yr)[0] < tol
 
 
-@pytest.mark.parametrize("mode", ["two_pass", "chained"])
+@pytest.mark.parametrize("mode", ["look_back", "chained"])
 def test_static_scratch_entry_with_the_tensor_core_kernels_twice(mode):
-    """The tensor-core kernels use the shared array in two ways: the two-pass scan keeps per-segment states in it,
-    the single-launch scan hands states from CTA to CTA through it and needs its ready flags cleared (the entry
-    point does that itself).  Two calls in a row on different data, against the ordinary entry point."""
+    """The tensor-core kernel passes states from CTA to CTA through the shared array, in two ways: with fewer
+    sequences than SMs every CTA publishes the state of its last piece scanned from zero and later pieces fold
+    those ("look-back"); with more, a piece hands its final state to the next ("chained").  Both need their ready
+    flags cleared, which the entry point does itself.  Two calls in a row on different data, against the ordinary
+    entry point."""
     import workloadsuite_b200 as W
     from workloadsuite_b200 import _lib
 
     lib = _lib.load()
-    if mode == "two_pass":      # 8 head pairs for 148 SMs: segments scanned concurrently, then folded
+    if mode == "look_back":     # 4 head pairs of 16 tiles for 148 SMs
         shape, nseg = dict(b=2, s=2048, h=4, p=64, n=128, g=1), 4
     else:                       # 160 head pairs: tiles dealt out evenly inside one launch
         shape, nseg = dict(b=40, s=512, h=8, p=64, n=128, g=2), 2
@@ -78,7 +80,7 @@ def test_static_scratch_entry_with_the_tensor_core_kernels_twice(mode):
         inp = O.make_inputs(dtype=torch.bfloat16, init=True, seed=seed, decay_scale=0.02, **shape)
         d = {k: v.to(DEV) for k, v in inp.items()}
         plan = W.plan(d["X"], d["A"], d["B"], d["C"], 256, kernel="tcgen05", nsegments=nseg)
-        assert plan["launches"] == (3 if mode == "two_pass" else 1) and 0 < plan["workspace_bytes"] <= 16 << 20
+        assert plan["launches"] == 1 and 0 < plan["workspace_bytes"] <= 16 << 20
         want = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], 256, initial_states=d["initial_states"],
                              kernel="tcgen05", nsegments=nseg)
         got = torch.empty_like(want)

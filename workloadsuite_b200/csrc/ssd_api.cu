@@ -154,7 +154,7 @@ int ssd_b200_plan(const SsdArgs* args, int32_t* kernel_out, int32_t* nsegments_o
   const bool state_only = (args->flags & SSD_FLAG_STATE_ONLY) != 0;
   int launches = 1;
   if (nseg > 1) {
-    const bool chained = kernel == SSD_KERNEL_TCGEN05 && use_tc2(args) && ssd::tc2_chain_segments(*args, nseg);
+    const bool chained = kernel == SSD_KERNEL_TCGEN05 && use_tc2(args) && ssd::tc2_chain_mode(*args, nseg) != 0;
     launches = chained ? 1 : (state_only ? 2 : 3);
     if (!chained && (args->flags & SSD_FLAG_REUSE_SEGMENTS)) launches -= 1;
   }
@@ -172,8 +172,8 @@ size_t ssd_b200_workspace_bytes(const SsdArgs* args) {
   if (nseg <= 1) return 0;
   const size_t units = (size_t)args->batch * args->nheads;
   const size_t np = (size_t)args->dstate * args->headdim;
-  if (kernel == SSD_KERNEL_TCGEN05 && use_tc2(args) && ssd::tc2_chain_segments(*args, nseg)) {
-    // chained mode: one hand-over slot per CTA and head of the pair -- state, log-decay sum, ready flag
+  if (kernel == SSD_KERNEL_TCGEN05 && use_tc2(args) && ssd::tc2_chain_mode(*args, nseg) != 0) {
+    // chained / look-back mode: one slot per CTA and head of the pair -- state, log-decay sum, ready flag
     const size_t slots = 2 * (size_t)kSmCount;
     return align_up(slots * np * sizeof(float), 256) + 2 * align_up(slots * sizeof(float), 256);
   }
@@ -221,8 +221,9 @@ static int forward_impl(const SsdArgs* args, void* stream_v, bool fuse_epilogue)
   const size_t need = ssd_b200_workspace_bytes(args);
   if (!args->workspace || args->workspace_bytes < need) return SSD_ERR_WORKSPACE;
   if (reinterpret_cast<uintptr_t>(args->workspace) & 255) return SSD_ERR_MISALIGNED;
-  if (kernel == SSD_KERNEL_TCGEN05 && use_tc2(args) && ssd::tc2_chain_segments(*args, nseg)) {
-    // one launch: the pieces of a sequence hand their state over through the workspace, one slot per CTA and head
+  const int chain_mode = (kernel == SSD_KERNEL_TCGEN05 && use_tc2(args)) ? ssd::tc2_chain_mode(*args, nseg) : 0;
+  if (chain_mode != 0) {
+    // one launch: the pieces of a sequence pass their state through the workspace, one slot per CTA and head
     const size_t slots = 2 * (size_t)kSmCount;
     char* ws = static_cast<char*>(args->workspace);
     float* slot_state = reinterpret_cast<float*>(ws);
@@ -232,7 +233,7 @@ static int forward_impl(const SsdArgs* args, void* stream_v, bool fuse_epilogue)
     if (cudaMemsetAsync(flags, 0, slots * sizeof(int32_t), stream) != cudaSuccess) return SSD_ERR_CUDA;
     ssd::ScanParams pc = prm;
     pc.compute_y = state_only ? 0 : 1;
-    pc.chain = 1;
+    pc.chain = chain_mode;
     pc.chain_state = slot_state;
     pc.chain_ld = slot_ld;
     pc.chain_flag = flags;

@@ -43,8 +43,10 @@ struct ScanParams {
   int vec_ok;          // all row starts 16-byte aligned
   long long wait_clocks;   // bound of every device-side wait, in SM clock cycles
   int inject_lost_handover;   // SSD_FLAG_INJECT_LOST_HANDOVER: CTA 0 of a chained launch leaves without working
-  // Chained mode (two-head tensor-core kernel only): a piece of a sequence starts from the state that the
+  // Chained mode (two-head tensor-core kernel only; 1): a piece of a sequence starts from the state that the
   // piece before it (on the neighbouring CTA) left in chain_state, once chain_flag says it is there.
+  // Look-back mode (2): chain_state / chain_ld hold each CTA's state-from-zero and log-decay sum of the last
+  // piece of its range; a piece folds those of the CTAs before it.
   int chain;
   float* chain_state;     // [slot][n*p], slot = 2 * CTA + head of the pair
   float* chain_ld;        // [slot] running sum of the log-decay up to the end of the piece
@@ -92,7 +94,7 @@ int launch_tc(const SsdArgs& a, const ScanParams& prm, cudaStream_t stream);
 // two-heads-per-CTA tcgen05 kernel (ssd_tc2.cu): needs an even number of heads per B/C group
 bool tc2_supports(const SsdArgs& a);
 int tc2_default_segments(const SsdArgs& a);
-bool tc2_chain_segments(const SsdArgs& a, int nseg);   // true: one chained pass; false: two passes + fold
+int tc2_chain_mode(const SsdArgs& a, int nseg);   // 1: chained, 2: look-back (one launch each); 0: two passes + fold
 int launch_tc2(const SsdArgs& a, const ScanParams& prm, cudaStream_t stream);
 
 

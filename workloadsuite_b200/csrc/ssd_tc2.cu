@@ -54,16 +54,25 @@ struct Layout2 {
 
 // Work list of this CTA.
 //  - Regular mode: items blockIdx.x, blockIdx.x + gridDim.x, ... of the (segment, sequence) grid.
-//  - Chained mode (sp.chain): all tiles of all sequences, laid end to end, are cut into gridDim.x equal ranges,
-//    so every CTA gets the same number of tiles (+-1) whatever the number of sequences.  A range holds the
-//    tail of one sequence, whole sequences and the head of another; they are walked in reverse, head first:
+//  - Chained mode (sp.chain == 1): all tiles of all sequences, laid end to end, are cut into gridDim.x equal
+//    ranges, so every CTA gets the same number of tiles (+-1) whatever the number of sequences.  A range holds
+//    the tail of one sequence, whole sequences and the head of another; they are walked in reverse, head first:
 //    the head's state is what the next CTA's tail piece waits for, and a tail piece (walked last) then finds
 //    the state it needs already there when there is at least one sequence per CTA.
+//  - Look-back mode (sp.chain == 2), for fewer sequences than CTAs: the same even cut, but a piece cannot wait
+//    for the full scan of the piece before it (the pieces of one sequence would run one after the other).
+//    Instead every CTA first scans the LAST piece of its range from a zero state, state and log-decay sum only
+//    (about 0.4 of the full work; item 0, skipped when that piece ends its sequence), and publishes the pair.
+//    Then it walks its pieces like the chained mode; a piece that starts inside a sequence folds the published
+//    pairs of the CTAs before it, back to the one that holds the sequence's first tile (the recurrence is linear:
+//    H_in = sum_c exp(sum of the log-decays after c) F_c), and stops early once the decay factor has underflowed.
 // Computed once per CTA (thread 0, into shared memory): the 64-bit divisions are bulky code.
 struct Work {
   int count;
   int lo, hi, nt, pl;   // chained mode: global tile range, tiles per sequence, last sequence of the range
   int hp, hpg;          // head pairs per batch entry, heads per B/C group
+  int pre;              // look-back mode: 1 when item 0 is the state-only scan of the range's last piece
+  int ytot;             // tiles of all Y-producing items
 };
 
 struct Misc2 {
@@ -98,6 +107,9 @@ struct Tc2Params {
 // continues on a neighbouring CTA (-1: the sequence starts / ends here).
 struct Item {
   int seg, bi, h0, gi, t_begin, ntiles, in_slot, out_slot;
+  int yflag;      // this item produces Y (0: state and log-decay sum only)
+  int fold_from;  // look-back mode: first CTA whose published pair enters the fold (-1: none), up to in_slot
+  int ends_seq;   // the item holds the last tile of its sequence: it writes the caller's final state
 };
 
 __device__ __forceinline__ void work_list(const Tc2Params& prm, Work* out) {
@@ -113,9 +125,13 @@ __device__ __forceinline__ void work_list(const Tc2Params& prm, Work* out) {
     wk.hi = (int)((long long)(blockIdx.x + 1) * total / gridDim.x);
     wk.pl = wk.hi > wk.lo ? (wk.hi - 1) / wk.nt : 0;
     wk.count = wk.hi > wk.lo ? wk.pl - wk.lo / wk.nt + 1 : 0;
+    wk.pre = (prm.sp.chain == 2 && wk.hi > wk.lo && wk.hi % wk.nt != 0) ? 1 : 0;
+    wk.count += wk.pre;
   } else {
+    wk.pre = 0;
     wk.count = (int)blockIdx.x < prm.nitems ? (prm.nitems - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
   }
+  wk.ytot = 0;
   *out = wk;
 }
 
@@ -123,14 +139,35 @@ __device__ __forceinline__ Item work_item(const Tc2Params& prm, const Work& wk, 
   const ScanParams& sp = prm.sp;
   Item it;
   int u2;
+  it.yflag = sp.compute_y;
+  it.fold_from = -1;
+  it.ends_seq = 1;
   if (sp.chain) {
-    u2 = wk.pl - i;
+    const bool pre = wk.pre && i == 0;        // look-back mode: the state-only scan of the last piece
+    u2 = wk.pl - (pre ? 0 : i - wk.pre);
     const int first = u2 * wk.nt, start = max(wk.lo, first), end = min(wk.hi, first + wk.nt);
     it.seg = 0;
     it.t_begin = (start - first) * T;
     it.ntiles = end - start;
     it.in_slot = start > first ? (int)blockIdx.x - 1 : -1;
     it.out_slot = end < first + wk.nt ? (int)blockIdx.x : -1;
+    it.ends_seq = end == first + wk.nt;
+    if (sp.chain == 2) {
+      if (pre) {
+        it.yflag = 0;
+        it.in_slot = -1;                      // from a zero state
+      } else {
+        it.out_slot = -1;                     // only the state-only scan publishes
+        if (it.in_slot >= 0) {
+          // the CTA that holds the sequence's first tile: the largest c with lo(c) <= first
+          const long long total = (long long)prm.upairs * wk.nt;
+          int c = (int)((((long long)first + 1) * gridDim.x - 1) / total);
+          while (c > 0 && (long long)c * total / gridDim.x > first) --c;
+          while ((long long)(c + 1) * total / gridDim.x <= first) ++c;
+          it.fold_from = c;
+        }
+      }
+    }
   } else {
     const int item = blockIdx.x + i * gridDim.x;
     it.seg = item / prm.upairs;
@@ -171,23 +208,6 @@ __device__ __forceinline__ void drain_mmas(Misc2* m, int which) {
     if (clock64() - t0 > m->wait_clocks) break;
 }
 
-#ifdef SSD_TC2_TRACE
-// debug build: time stamps of pipeline events of CTA 0 for tiles [kTr0, kTr0+kTrN) into status[256...]
-#ifndef SSD_TC2_TRACE_FIRST
-#define SSD_TC2_TRACE_FIRST 20
-#endif
-constexpr int kTr0 = SSD_TC2_TRACE_FIRST, kTrN = 6, kTrEv = 24;
-#define TRACE(ev, tile) { if (blockIdx.x == 0 && status && (int)(tile) >= kTr0 && (int)(tile) < kTr0 + kTrN) \
-    status[256 + ((int)(tile) - kTr0) * kTrEv + (ev)] = (int)(clock64() & 0x7fffffff); }
-#else
-#define TRACE(ev, tile) {}
-#endif
-#ifdef SSD_TC2_TRACE
-#define ITRACE(idx) { if ((blockIdx.x == 0 || blockIdx.x == gridDim.x - 1) && status && (idx) < 32) \
-    status[128 + (blockIdx.x == 0 ? 0 : 32) + (idx)] = (int)(clock64() & 0x7fffffff); }
-#else
-#define ITRACE(idx) {}
-#endif
 
 // EPI: apply the skip and gate of model_ref.py:116-118 to Y on its way out (sp.D / sp.Z; either may be null).
 template <typename T16, int N, bool EPI>
@@ -213,15 +233,11 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool want_y = sp.compute_y != 0;
   int32_t* status = sp.status;
-  if (tid == 0) ITRACE(0)
-#ifdef SSD_TC2_TRACE
-  if (tid == 0 && status) { unsigned long long g; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(g)); status[400 + blockIdx.x] = (int)(g & 0x7fffffff); }
-#endif
 
   if (tid == 0) {
     mbar_init(&m->full_b, 1); mbar_init(&m->full_c, 1);
     // B is released by the G MMA and the S MMA; C by the G MMA and the C.H MMA
-    mbar_init(&m->empty_b, want_y ? 2 : 1); mbar_init(&m->empty_c, 2);
+    mbar_init(&m->empty_b, want_y ? 2 : 1); mbar_init(&m->empty_c, 2);   // (a state-only item inside a Y launch: the S issuer commits twice)
     mbar_init(&m->bar_g, 1);
     mbar_init(&m->bar_yo, 1); mbar_init(&m->bar_s, 1);
     mbar_init(&m->bar_xd, 8); mbar_init(&m->bar_h, 8); mbar_init(&m->bar_e, 8);
@@ -230,7 +246,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       // has served as the source of the TMA store of Y)
       for (int s = 0; s < kXStages; ++s) {
         mbar_init(&m->full_x[h][s], 1);
-        mbar_init(&m->empty_x[h][s], want_y ? 1 : 4);   // Y mode: the thread that issued the TMA store of Y
+        mbar_init(&m->empty_x[h][s], 4);   // Y items: the thread that issued the TMA store of Y arrives for all four
       }
       mbar_init(&m->bar_y[h], 1);
       mbar_init(&m->bar_p[h], 4);   // one arrival per compute warp (lane 0, after a warp barrier)
@@ -239,6 +255,10 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     m->abort_flag = 0;
     m->wait_clocks = sp.wait_clocks;
     work_list(prm, &m->work);
+    for (int i = 0; i < m->work.count; ++i) {
+      const Item wi = work_item(prm, m->work, i);
+      if (wi.yflag) m->work.ytot += wi.ntiles;
+    }
     fence_mbar_init();
   }
   if (warp == 0) tmem_alloc(&m->tmem_base, 512);
@@ -256,7 +276,8 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       // ---------------------------------------------------------------- TMA producer
       prefetch_tmap(&tmX); prefetch_tmap(&tmB); prefetch_tmap(&tmC); prefetch_tmap(&tmY);
       bool ok = true;
-      uint32_t it = 0;   // running tile ordinal of this CTA
+      uint32_t it = 0;    // running tile ordinal of this CTA
+      uint32_t ity = 0;   // ... counting the tiles of Y-producing items only (C is loaded for those)
       const Work wk = m->work;
       for (int wi = 0; wi < wk.count && ok; ++wi) {
         const Item w = work_item(prm, wk, wi);
@@ -268,17 +289,16 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             if (!ok) break;
             mbar_expect_tx(&m->full_x[h][st], kBlk);
             tma_load_4d(smem + L::oX + (kXStages * h + st) * kBlk, &tmX, &m->full_x[h][st], 0, w.h0 + h, t0, w.bi);
-            if (h == 0) TRACE(14, it)
           }
           if (!ok) break;
-          if (want_y) {
-            if (it > 0) ok = wait2(&m->empty_c, (it - 1) & 1, m, STATUS_WAIT_TIMEOUT_MMA, status);
+          if (w.yflag) {
+            if (ity > 0) ok = wait2(&m->empty_c, (ity - 1) & 1, m, STATUS_WAIT_TIMEOUT_MMA, status);
             if (!ok) break;
             mbar_expect_tx(&m->full_c, NB * kBlk);
 #pragma unroll
             for (int kb = 0; kb < NB; ++kb)
               tma_load_4d(smem + L::oC + kb * kBlk, &tmC, &m->full_c, 64 * kb, w.gi, t0, w.bi);
-            TRACE(15, it)
+            ++ity;
           }
           if (it > 0) ok = wait2(&m->empty_b, (it - 1) & 1, m, STATUS_WAIT_TIMEOUT_MMA, status);
           if (!ok) break;
@@ -286,7 +306,6 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 #pragma unroll
           for (int kb = 0; kb < NB; ++kb)
             tma_load_4d(smem + L::oB + kb * kBlk, &tmB, &m->full_b, 64 * kb, w.gi, t0, w.bi);
-          TRACE(16, it)
         }
       }
       if (m->abort_flag && it > 0) {
@@ -296,7 +315,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         while (clock64() - c0 < 2000000LL) {
           const uint32_t xs = k % kXStages, xp = (k / kXStages) & 1;
           if (mbar_try_wait(&m->full_b, k & 1) && mbar_try_wait(&m->full_x[0][xs], xp) &&
-              mbar_try_wait(&m->full_x[1][xs], xp) && (!want_y || mbar_try_wait(&m->full_c, k & 1)))
+              mbar_try_wait(&m->full_x[1][xs], xp) && (ity == 0 || mbar_try_wait(&m->full_c, (ity - 1) & 1)))
             break;
         }
       }
@@ -306,17 +325,19 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         constexpr int fmt = std::is_same<T16, __nv_bfloat16>::value ? 1 : 0;
         constexpr uint32_t idG = umma_idesc(128, 128, fmt, 0, 0);
         constexpr uint64_t dK = umma_desc_base(16, 1024);
-        uint32_t ttot = 0;
         const Work wk = m->work;
-        for (int wi = 0; wi < wk.count; ++wi) ttot += work_item(prm, wk, wi).ntiles;
         bool ok = true;
-        for (uint32_t k = 0; k < ttot && ok; ++k) {
+        uint32_t it = 0, k = 0;   // tile ordinal over all items / over the Y-producing ones
+        for (int wi = 0; wi < wk.count && ok; ++wi) {
+          const Item w = work_item(prm, wk, wi);
+          if (!w.yflag) { it += w.ntiles; continue; }
+        for (int j = 0; j < w.ntiles && ok; ++j, ++it, ++k) {
           // both heads are done reading G(k-1); B and C of tile k have landed
           if (k > 0)
             ok = wait2(&m->bar_p[0], (k - 1) & 1, m, STATUS_WAIT_TIMEOUT_SYNC, status) &&
                  wait2(&m->bar_p[1], (k - 1) & 1, m, STATUS_WAIT_TIMEOUT_SYNC, status);
           ok = ok && wait2(&m->full_c, k & 1, m, STATUS_WAIT_TIMEOUT_TMA, status) &&
-               wait2(&m->full_b, k & 1, m, STATUS_WAIT_TIMEOUT_TMA, status);
+               wait2(&m->full_b, it & 1, m, STATUS_WAIT_TIMEOUT_TMA, status);
           if (!ok) break;
           tc_fence_after();
 #pragma unroll
@@ -324,10 +345,10 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             const uint32_t off = (kk >> 2) * kBlk + (kk & 3) * 32;
             umma_ss(tG, umma_desc(dK, sC + off), umma_desc(dK, sB + off), idG, kk > 0);
           }
-          TRACE(13, k)
           umma_commit(&m->bar_g);
           umma_commit(&m->empty_c);
           umma_commit(&m->empty_b);
+        }
         }
       }
       drain_mmas(m, 0);
@@ -344,9 +365,11 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       const uint32_t tS = tb + 128, tY = tb + 256;
       bool ok = true;
       uint32_t k0 = 0;   // running tile ordinal of the item's first tile
+      uint32_t ky = 0;   // tile ordinal over the Y-producing items
       const Work wk = m->work;
       for (int wi = 0; wi < wk.count && ok; ++wi) {
-        const int nt = work_item(prm, wk, wi).ntiles;
+        const Item w = work_item(prm, wk, wi);
+        const int nt = w.ntiles;
 #pragma unroll 1
         for (int j = 0; j < nt && ok; ++j) {
           const uint32_t k = k0 + j;
@@ -354,28 +377,29 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           ok = wait2(&m->full_b, k & 1, m, STATUS_WAIT_TIMEOUT_TMA, status) &&
                wait2(&m->bar_xd, k & 1, m, STATUS_WAIT_TIMEOUT_SYNC, status);
           if (!ok) break;
-          TRACE(22, k)
           tc_fence_after();
 #pragma unroll
           for (int kk = 0; kk < KT; ++kk)
             umma_ss(tS, umma_desc(dMN, sB + kk * 2048), umma_desc(dMN, sXd + kk * 2048), idMM, kk > 0);
-          TRACE(10, k)
           umma_commit(&m->bar_s);
           umma_commit(&m->empty_b);
-          if (!want_y) continue;
+          if (!w.yflag) {
+            // (a state-only item inside a Y launch: no G MMA reads this B tile, its arrival is made here)
+            if (want_y) umma_commit(&m->empty_b);
+            continue;
+          }
           // Y <- C . H
-          ok = wait2(&m->full_c, k & 1, m, STATUS_WAIT_TIMEOUT_TMA, status) &&
-               wait2(&m->bar_h, k & 1, m, STATUS_WAIT_TIMEOUT_SYNC, status);
-          if (ok && k > 0) ok = wait2(&m->bar_e, (k - 1) & 1, m, STATUS_WAIT_TIMEOUT_SYNC, status);
+          ok = wait2(&m->full_c, ky & 1, m, STATUS_WAIT_TIMEOUT_TMA, status) &&
+               wait2(&m->bar_h, ky & 1, m, STATUS_WAIT_TIMEOUT_SYNC, status);
+          if (ok && ky > 0) ok = wait2(&m->bar_e, (ky - 1) & 1, m, STATUS_WAIT_TIMEOUT_SYNC, status);
           if (!ok) break;
-          TRACE(21, k)
+          ++ky;
           tc_fence_after();
 #pragma unroll
           for (int kk = 0; kk < KN; ++kk) {
             const uint32_t off = (kk >> 2) * kBlk + (kk & 3) * 32;
             umma_ss(tY, umma_desc(dK, sC + off), umma_desc(dMNh, sH + kk * 2048), idKM, kk > 0);
           }
-          TRACE(12, k)
           umma_commit(&m->bar_yo);
           umma_commit(&m->empty_c);
         }
@@ -388,27 +412,28 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         constexpr int fmt = std::is_same<T16, __nv_bfloat16>::value ? 1 : 0;
         constexpr uint32_t idKM = umma_idesc(128, 64, fmt, 0, 1);
         constexpr uint64_t dMN = umma_desc_base(kBlk, 1024);
-        uint32_t ttot = 0;
         const Work wk = m->work;
-        for (int wi = 0; wi < wk.count; ++wi) ttot += work_item(prm, wk, wi).ntiles;
         bool ok = true;
+        uint32_t it = 0, k = 0;   // tile ordinal over all items / over the Y-producing ones
+        for (int wi = 0; wi < wk.count && ok; ++wi) {
+          const Item w = work_item(prm, wk, wi);
+          if (!w.yflag) { it += w.ntiles; continue; }
 #pragma unroll 1
-        for (uint32_t k = 0; k < ttot && ok; ++k) {
-          const uint32_t st = k % kXStages;
+        for (int j = 0; j < w.ntiles && ok; ++j, ++it, ++k) {
+          const uint32_t st = it % kXStages;
 #pragma unroll 1
           for (int h = 0; h < 2 && ok; ++h) {
             ok = wait2(&m->bar_p[h], k & 1, m, STATUS_WAIT_TIMEOUT_SYNC, status) &&
-                 wait2(&m->full_x[h][st], (k / kXStages) & 1, m, STATUS_WAIT_TIMEOUT_TMA, status);
+                 wait2(&m->full_x[h][st], (it / kXStages) & 1, m, STATUS_WAIT_TIMEOUT_TMA, status);
             if (!ok) break;
-            if (h == 0) TRACE(20, k)
             tc_fence_after();
             const uint32_t tY = tb + 256 + 64 * h, tP = tb + 384 + 64 * h;
 #pragma unroll
             for (int kk = 0; kk < KT; ++kk)
               umma_ts(tY, tP + 8 * kk, umma_desc(dMN, sX + (kXStages * h + st) * kBlk + kk * 2048), idKM, 1);
-            if (h == 0) TRACE(11, k)
             umma_commit(&m->bar_y[h]);
           }
+        }
         }
       }
       drain_mmas(m, 2);
@@ -427,7 +452,8 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     const uint32_t sHh = sH + h * (N * 128), sXdh = sXd + h * kBlk;
     const int bar_id = 1 + h;
 
-    uint32_t it = 0;   // running tile ordinal of this CTA
+    uint32_t it = 0;    // running tile ordinal of this CTA
+    uint32_t ity = 0;   // ... counting the tiles of Y-producing items only
     bool ok = true;
     auto cwait = [&](uint64_t* bar, uint32_t parity, int code) {
       return __all_sync(0xffffffffu, wait2(bar, parity, m, code, status)) != 0;
@@ -439,14 +465,6 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       if (lane == 0) mbar_arrive(bar);
     };
 
-#ifdef SSD_TC2_PROFILE
-    long long prof[24] = {};
-    long long pt = clock64();
-#define PROF(i) { const long long pn = clock64(); prof[i] += pn - pt; pt = pn; }
-#else
-#define PROF(i)
-#endif
-#define CTRACE(ev) { if (h == 0 && l == 96) TRACE(ev, it) }
     float H[P];
     float cs = 0.f, tot = 0.f, cs2 = 0.f;   // of the tile whose P / Y is being produced
     // dt multiplies the columns of P instead of the rows of X (P.(dt o x) = (P o dt_s).x), so the X tile stays as
@@ -469,9 +487,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         if (lane >= d) v += t;
       }
       if (lane == 31) m->wsum[h][q] = v;
-      PROF(11)
       named_bar_sync(bar_id, 128);
-      PROF(12)
       const float w0 = m->wsum[h][0], w1 = m->wsum[h][1], w2 = m->wsum[h][2], w3 = m->wsum[h][3];
       cs_o = v + ((q > 0 ? w0 : 0.f) + (q > 1 ? w1 : 0.f) + (q > 2 ? w2 : 0.f));
       tot_o = (w0 + w1 + w2) + w3;
@@ -484,7 +500,6 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       // cf / cend are read one tile later and the warp sums are rewritten one tile later: the barrier of the Y
       // read-out lies in between, except after an item's first tile and in state-only mode
       if (sync_after) named_bar_sync(bar_id, 128);
-      PROF(13)
     };
     // Xd = exp(cs_last - cs_l) * dt * x (model_ref.py:144,148) from X stage `st` into this head's Xd buffer
     auto make_xd = [&](uint32_t st, float cs_t, float tot_t, float dtv) {
@@ -519,10 +534,9 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     // ---- e. Y -> global, for the tile whose P.X MMA was started one step earlier (its latency is spent in the
     //      next tile's state update).  Returns false when a wait gave up.
     bool y_pending = false;
-    uint32_t y_it = 0;
+    uint32_t y_it = 0, y_ity = 0;
     int y_hi = 0, y_t0 = 0, y_bi = 0;
     auto finish_y = [&]() -> bool {
-      PROF(20)
       // (EPI) the gate rows of this warp's 32 tokens, fetched ahead of the wait for the MMA.  Eight lanes read one
       // 128-byte row per load (whole lines), four rows per instruction; the rows reach their threads through the
       // staging buffer below.
@@ -537,9 +551,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           }
         }
       }
-      if (!cwait(&m->bar_y[h], y_it & 1, STATUS_WAIT_TIMEOUT_MMA)) return false;
-      if (h == 0 && l == 96) TRACE(8, y_it)
-      PROF(17)
+      if (!cwait(&m->bar_y[h], y_ity & 1, STATUS_WAIT_TIMEOUT_MMA)) return false;
       tc_fence_after();
       // The X stage of that tile is dead (its P.X MMA is complete): stage the 16-bit Y rows there; one
       // thread then hands the whole tile to the TMA engine.
@@ -550,9 +562,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         tmem_ld32(tY + tlane, y0);
         tmem_ld32(tY + tlane + 32, y1);
         tmem_ld_wait();
-      PROF(18)
         tc_fence_before();
-        if (h == 0 && l == 96) TRACE(9, y_it)
         warp_arrive(&m->bar_e);   // the Y accumulator is read out: the next tile's C.H may overwrite it
         if constexpr (EPI) {
           // Y <- (Y + x * D) * silu(z) (model_ref.py:116-118) in fp32; x is this thread's row of the X tile, still in
@@ -619,22 +629,19 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           sts128(ystage + l * 128 + (((4 + c) ^ swz) << 4), o);
         }
       }
-      PROF(19)
       fence_proxy_async();         // staged rows -> visible to the TMA engine
       named_bar_sync(bar_id, 128);
       if (l == 0) {
         // The previous store must be done reading its stage before the producer may refill it.
         if (store_pending) {
           bulk_wait_read_all();
-          mbar_arrive(&m->empty_x[h][store_stage]);
+          mbar_arrive_n(&m->empty_x[h][store_stage], 4);
         }
         tma_store_4d(&tmY, ystage, 0, y_hi, y_t0, y_bi);
         bulk_commit();
         store_pending = true;
         store_stage = xst;
       }
-      if (h == 0 && l == 96) TRACE(17, y_it)
-      PROF(21)
       y_pending = false;
       return true;
     };
@@ -646,8 +653,8 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       Item w = {};
       if (wi < wk.count) w = work_item(prm, wk, wi);
       if (w.ntiles == 0 && wi < wk.count) continue;
-      if (h == 0 && l == 96) ITRACE(1 + wi)
       const int hi = w.h0 + h;
+      const bool wy = w.yflag != 0;   // this item produces Y (a look-back launch starts with a state-only item)
       const int64_t unit = (int64_t)w.bi * sp.nheads + hi;
       const float* Ag = sp.A + w.bi * sp.as[0] + hi * sp.as[2];
       const T16* Dg = sp.dt ? static_cast<const T16*>(sp.dt) + w.bi * sp.dts[0] + hi * sp.dts[2] : nullptr;
@@ -665,18 +672,14 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       // tile j (steps a, b, d, e) and prepares tile j + 1 (step c) in between, so that the S MMA of the
       // next tile runs under steps d and e.  One copy of each step keeps the loop inside the
       // instruction cache.
-        PROF(23)
 #pragma unroll 1
       for (int j = -1; j < w.ntiles && ok; ++j) {
         const int t0 = w.t_begin + j * T;
         const bool have_next = (j + 1 < w.ntiles);
         if (j >= 0) {
           // ---- a. state: H <- exp(cs_last) H + S
-        PROF(22)
           ok = cwait(&m->bar_s, it & 1, STATUS_WAIT_TIMEOUT_MMA);
           if (!ok) break;
-          CTRACE(0)
-        PROF(0)
           tc_fence_after();
           {
             const float yk = tot - acomp, tk = asum + yk;
@@ -689,13 +692,11 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             tmem_ld32(tS + tlane, sv0);
             tmem_ld32(tS + tlane + 32, sv1);
             tmem_ld_wait();
-        PROF(1)
 #pragma unroll
             for (int e = 0; e < 32; ++e) H[e] = fmaf(H[e], g, __uint_as_float(sv0[e]));
 #pragma unroll
             for (int e = 0; e < 32; ++e) H[32 + e] = fmaf(H[32 + e], g, __uint_as_float(sv1[e]));
           }
-        PROF(2)
         }
         // ---- state leaving the item: it is final once the last tile's update (step a) is done, so it is
         //      handed over here, ahead of the rest of that tile; the next item's first log-decays are fetched too
@@ -716,7 +717,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
               const int one = 1;
               asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(sp.chain_flag + slot), "r"(one) : "memory");
             }
-          } else {
+          } else if (w.ends_seq) {
             // last (or only) segment of the sequence: the caller's outputs
             const int fseg = sp.chain ? 0 : w.seg;
             if (sp.fin && owns_state) {
@@ -753,24 +754,67 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             a_next = Ag[(int64_t)(t0 + 2 * T + l) * sp.as[1]];
             if (Dg) dt_next = Cvt<T16>::to_f(Dg[(int64_t)(t0 + 2 * T + l) * sp.dts[1]]);
           }
-          scan_tile(a, dtv, itn & 1, j < 0 || !want_y, cs_n, tot_n, cs2_n, cs2c_n);
-          if (h == 0 && l == 96) TRACE(18, itn)
+          scan_tile(a, dtv, itn & 1, j < 0 || !wy, cs_n, tot_n, cs2_n, cs2c_n);
           ok = cwait(&m->full_x[h][itn % kXStages], (itn / kXStages) & 1, STATUS_WAIT_TIMEOUT_TMA);
           if (!ok) break;
-          if (h == 0 && l == 96) TRACE(19, itn)
-        PROF(14)
           make_xd(itn % kXStages, cs_n, tot_n, dtv);
-        PROF(15)
           fence_proxy_async();
           warp_arrive(&m->bar_xd);
-          if (h == 0 && l == 96) TRACE(2, itn)
-          if (!want_y) warp_arrive(&m->empty_x[h][itn % kXStages]);   // nothing else reads X in state-only mode
+          if (!wy) warp_arrive(&m->empty_x[h][itn % kXStages]);   // nothing else reads X of a state-only item
         }
-        PROF(16)
         // ---- state entering the item (after the first tile's Xd is on its way to the S MMA: the wait for a
         //      chained predecessor and the state load then overlap that MMA)
         if (j == -1 && w.ntiles > 0) {
-          if (w.in_slot >= 0) {
+          if (w.in_slot >= 0 && sp.chain == 2) {
+            // Look-back: fold the pairs (state from zero, log-decay sum) that the CTAs fold_from..in_slot published
+            // for their pieces of this sequence, newest first: H_in = sum_c exp(log-decay after c) F_c (+ the same
+            // for the caller's initial state).  Wait (bounded) until all of them are there.
+            if (l == 0) {
+              const long long c0 = clock64();
+              for (int c = w.in_slot; c >= w.fold_from && !m->abort_flag; --c) {
+                while (true) {
+                  int f;
+                  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(f) : "l"(sp.chain_flag + 2 * c + h) : "memory");
+                  if (f >= 4) break;   // all four warps of that CTA's warpgroup have published
+                  if (m->abort_flag) break;
+                  if (clock64() - c0 > m->wait_clocks) {
+                    m->abort_flag = (int)STATUS_WAIT_TIMEOUT_CHAIN;
+                    break;
+                  }
+                }
+              }
+            }
+            named_bar_sync(bar_id, 128);
+            if (m->abort_flag) { ok = false; break; }
+#pragma unroll
+            for (int e = 0; e < P; ++e) H[e] = 0.f;
+            float dsum = 0.f;   // log-decay between the end of the piece being added and the start of this one
+            for (int c = w.in_slot; c >= w.fold_from; --c) {
+              const int64_t slot = 2 * c + h;
+              const float wgt = ex2(dsum * kLog2e);
+              if (owns_state && wgt != 0.f) {   // (a piece whose weight has underflowed adds nothing)
+                const float4* I = reinterpret_cast<const float4*>(sp.chain_state + slot * (int64_t)(N * P) + (int64_t)l * P);
+#pragma unroll
+                for (int e = 0; e < P / 4; ++e) {
+                  const float4 v = __ldcg(I + e);   // written by another SM: bypass L1
+                  H[4 * e] = fmaf(wgt, v.x, H[4 * e]); H[4 * e + 1] = fmaf(wgt, v.y, H[4 * e + 1]);
+                  H[4 * e + 2] = fmaf(wgt, v.z, H[4 * e + 2]); H[4 * e + 3] = fmaf(wgt, v.w, H[4 * e + 3]);
+                }
+              }
+              dsum += __ldcg(sp.chain_ld + slot);
+            }
+            if (sp.init && owns_state) {
+              const float wgt = ex2(dsum * kLog2e);
+              const float4* I = reinterpret_cast<const float4*>(sp.init + unit * sp.init_unit_stride + (int64_t)l * P);
+#pragma unroll
+              for (int e = 0; e < P / 4; ++e) {
+                const float4 v = I[e];
+                H[4 * e] = fmaf(wgt, v.x, H[4 * e]); H[4 * e + 1] = fmaf(wgt, v.y, H[4 * e + 1]);
+                H[4 * e + 2] = fmaf(wgt, v.z, H[4 * e + 2]); H[4 * e + 3] = fmaf(wgt, v.w, H[4 * e + 3]);
+              }
+            }
+            asum0 = dsum;
+          } else if (w.in_slot >= 0) {
             // wait (bounded) for the previous segment of this unit, which another CTA may still be finishing
             const int64_t slot = 2 * w.in_slot + h;
             if (l == 0) {
@@ -800,7 +844,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
               for (int j = 0; j < P; ++j) H[j] = 0.f;
             }
             asum0 = __ldcg(sp.chain_ld + slot);
-          } else if (sp.init && owns_state) {
+          } else if (sp.init && owns_state && !(sp.chain == 2 && !wy)) {   // (the look-back scan starts from zero)
             const float4* I = reinterpret_cast<const float4*>(sp.init + unit * sp.init_unit_stride +
                                                               w.seg * sp.init_seg_stride + (int64_t)l * P);
     #pragma unroll
@@ -816,17 +860,14 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         if (l == 0 && store_pending) {
           // the Y store issued in the previous tile's step e has finished reading its stage by now: hand it back
           bulk_wait_read_all();
-          mbar_arrive(&m->empty_x[h][store_stage]);
+          mbar_arrive_n(&m->empty_x[h][store_stage], 4);
           store_pending = false;
         }
         if (j >= 0) {
-          if (want_y) {
+          if (wy) {
             // ---- d. P = (C B^T) o exp(segsum), causal -> TMEM (A operand, 16-bit pairs)
-            CTRACE(4)
-            ok = cwait(&m->bar_g, it & 1, STATUS_WAIT_TIMEOUT_MMA);
+            ok = cwait(&m->bar_g, ity & 1, STATUS_WAIT_TIMEOUT_MMA);
             if (!ok) break;
-            CTRACE(5)
-        PROF(8)
             tc_fence_after();
             const uint32_t par = it & 1;
             // Decay mask per 32-token column block J of this warp's 32 rows (block q is the diagonal one):
@@ -876,21 +917,17 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
               }
               tmem_st16(tP + tlane + 16 * J, pk);
             }
-            if (it == 0) {
+            if (ity == 0) {
               uint32_t pz[16];
 #pragma unroll
               for (int e = 0; e < 16; ++e) pz[e] = 0u;
 #pragma unroll 1
               for (int J = q + 1; J < 4; ++J) tmem_st16(tP + tlane + 16 * J, pz);
             }
-        PROF(9)
             // ---- b. Y <- exp(cs_l) * (C.H) in place (after P: the C.H MMA could only start once the previous
             //      tile's Y had been read out, so it runs under step d); the P.X MMA accumulates on top
-            CTRACE(1)
-            ok = cwait(&m->bar_yo, it & 1, STATUS_WAIT_TIMEOUT_MMA);
+            ok = cwait(&m->bar_yo, ity & 1, STATUS_WAIT_TIMEOUT_MMA);
             if (!ok) break;
-            CTRACE(3)
-        PROF(3)
             tc_fence_after();
             const float el = ex2(cs2);
             {
@@ -898,7 +935,6 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
               tmem_ld32(tY + tlane, y0);
               tmem_ld32(tY + tlane + 32, y1);
               tmem_ld_wait();
-        PROF(4)
 #pragma unroll
               for (int e = 0; e < 32; ++e) y0[e] = __float_as_uint(__uint_as_float(y0[e]) * el);
               tmem_st32(tY + tlane, y0);
@@ -906,27 +942,22 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
               for (int e = 0; e < 32; ++e) y1[e] = __float_as_uint(__uint_as_float(y1[e]) * el);
               tmem_st32(tY + tlane + 32, y1);
             }
-        PROF(5)
             tmem_st_wait();
-        PROF(6)
             tc_fence_before();
             warp_arrive(&m->bar_p[h]);   // P is written and Y is scaled: the P.X MMA may run
-            CTRACE(6)
-        PROF(10)
           }
         }
         // (all C.H MMAs that read the state copy have been waited for: the previous item's in its step b)
-        if (want_y && have_next) {
+        if (wy && have_next) {
           store_hb();
           fence_proxy_async();
           warp_arrive(&m->bar_h);
-          if (h == 0 && l == 96) TRACE(7, (j >= 0 ? it + 1 : it))
         }
-        PROF(7)
         if (j >= 0) {
-          if (want_y) {
+          if (wy) {
             y_pending = true;
-            y_it = it; y_hi = hi; y_t0 = t0; y_bi = w.bi;
+            y_it = it; y_ity = ity; y_hi = hi; y_t0 = t0; y_bi = w.bi;
+            ++ity;
           }
           ++it;
         }
@@ -935,22 +966,13 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       if (!ok) break;
 
     }
-    if (h == 0 && l == 96) ITRACE(30)
     if (l == 0) bulk_wait_all();   // the Y tiles this thread stored must have landed before the CTA exits
-#ifdef SSD_TC2_PROFILE
-    if (blockIdx.x == 0 && h == 0 && (l == 0 || l == 96) && status) {
-      for (int i = 0; i < 24; ++i) status[2 + 24 * (l / 96) + i] = (int)(prof[i] >> 4);   // cycles / 16
-    }
-#endif
   }
 
   // ---------------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
   if (tid == 0 && m->abort_flag && status) atomicCAS(status, 0, (int)m->abort_flag);
-#ifdef SSD_TC2_TRACE
-  if (tid == 0 && status) { unsigned long long g; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(g)); status[560 + blockIdx.x] = (int)(g & 0x7fffffff); }
-#endif
   if (warp == 0) {
     __syncwarp();
     tmem_dealloc(tb, 512);
@@ -985,12 +1007,19 @@ static double round_efficiency(int64_t items) {
   return (double)items / (double)(rounds * kSms);
 }
 
-// With at least one sequence per SM the tiles of all sequences are dealt out evenly over the CTAs inside one
-// launch; a sequence cut that way hands its state from CTA to CTA through scratch ("chained").  With fewer
-// sequences than SMs the cuts must be scanned concurrently instead: two passes and a fold.
-bool tc2_chain_segments(const SsdArgs& a, int nseg) {
+// How a sequence that is cut (nseg > 1) is scanned by this kernel:
+//   1  with at least one sequence per SM the tiles of all sequences are dealt out evenly over the CTAs inside one
+//      launch; a sequence cut that way hands its state from CTA to CTA through scratch ("chained");
+//   2  with fewer sequences than SMs the same even deal, but each CTA first scans the last piece of its range
+//      from zero and publishes (state, log-decay sum), and a piece folds what the CTAs before it published
+//      ("look-back"), still one launch;
+//   0  two passes and a fold (three launches): kept for the state-only run and the run that reuses its segment
+//      states, which a sequence-sharded forward makes around its exchange.
+int tc2_chain_mode(const SsdArgs& a, int nseg) {
+  if (nseg <= 1) return 0;
   const int64_t upairs = (int64_t)a.batch * a.nheads / 2;
-  return nseg > 1 && upairs >= kSms;
+  if (upairs >= kSms) return 1;
+  return (a.flags & (SSD_FLAG_STATE_ONLY | SSD_FLAG_REUSE_SEGMENTS)) ? 0 : 2;
 }
 
 int tc2_default_segments(const SsdArgs& a) {
@@ -999,11 +1028,18 @@ int tc2_default_segments(const SsdArgs& a) {
   // whole sequences already fill the rounds of the persistent grid well: no cuts; else the even deal (any count
   // above one selects it, the cut points follow from the grid)
   if (upairs >= kSms) return (round_efficiency(upairs) >= 0.97 || tiles < 2) ? 1 : 2;
+  const double whole = (double)tiles + 1.5;   // one CTA per sequence, in tile times
+  if (!(a.flags & (SSD_FLAG_STATE_ONLY | SSD_FLAG_REUSE_SEGMENTS))) {
+    // Look-back: every CTA gets total / SMs tiles plus the state-only scan of its last piece (0.4 of a full
+    // tile, on most of its range) and two item start-ups.
+    const double lookback = (double)upairs * tiles / kSms * 1.3 + 3.5;
+    return (tiles >= 2 && lookback < 0.95 * whole) ? 2 : 1;
+  }
   if (upairs >= 120) return 1;
-  // Fewer sequences than SMs: cutting them into concurrently scanned segments costs a second pass
+  // Two passes: cutting the sequences into concurrently scanned segments costs a second pass
   // (about 0.4 of a full pass) and a per-item start-up (about 1.5 tile times).  Pick the count that
   // minimises the modelled time, in tile times, of the busiest CTA.
-  double best_cost = (double)((upairs + kSms - 1) / kSms) * (tiles + 1.5);
+  double best_cost = whole;
   int best = 1;
   for (int nseg = 2; nseg <= 32 && nseg * 2 <= tiles; ++nseg) {
     const int64_t rounds = (upairs * nseg + kSms - 1) / kSms;

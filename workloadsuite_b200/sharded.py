@@ -202,10 +202,9 @@ class SequenceShardedSSD:
 
         kw = {k: v for k, v in kw.items() if k in ("kernel", "nsegments")}
         p_state = plan(X, A, B, C, chunk, state_only=True, **kw)
-        p_full = plan(X, A, B, C, chunk, **kw)
-        seeded = p_full["launches"] - 1 if p_full["nsegments"] > 1 and p_full["launches"] == 3 else p_full["launches"]
+        p_seeded = plan(X, A, B, C, chunk, reuse_segments=True, **kw)   # (already net of the reused first pass)
         fold = 1 if self.rank > 0 else 0
-        return p_state["launches"] + fold + seeded
+        return p_state["launches"] + fold + p_seeded["launches"]
 
     def phase_times_ms(self, repeats: int = 10):
         """CUDA-event times of the phases of the last ``forward`` (eager launches on the current stream, median over

@@ -338,11 +338,11 @@ def kernel_name(X, A, B, C_, chunk, kernel=None) -> str:
     return _lib.load().ssd_b200_kernel_name(C.byref(args)).decode()
 
 
-def plan(X, A, B, C_, chunk, kernel=None, nsegments=None, state_only=False) -> dict:
+def plan(X, A, B, C_, chunk, kernel=None, nsegments=None, state_only=False, reuse_segments=False) -> dict:
     """Kernel family, segments per sequence, kernel launches and scratch bytes ``ssd_forward`` uses."""
     _check(X, A, B, C_, None, None)
     args = _lib.SsdArgs()
-    _fill(args, X, A, B, C_, None, None, None, None, None, chunk, kernel, nsegments, state_only)
+    _fill(args, X, A, B, C_, None, None, None, None, None, chunk, kernel, nsegments, state_only, reuse_segments)
     lib = _lib.load()
     k, nseg, launches = C.c_int32(), C.c_int32(), C.c_int32()
     rc = lib.ssd_b200_plan(C.byref(args), C.byref(k), C.byref(nseg), C.byref(launches))
