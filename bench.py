@@ -511,6 +511,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-others", action="store_true")
+    ap.add_argument("--others", default="configs,skip_gate,conv,model",
+                    help="which single-GPU extras to time: configs, skip_gate, conv, model (comma-separated)")
     ap.add_argument("--no-parity", action="store_true", help="skip the parity leg (profiling runs only)")
     ap.add_argument("--no-model-compile", action="store_true",
                     help="skip the torch.compile variant of the reference Model (about a minute of compilation)")
@@ -632,9 +634,10 @@ def main():
             others[key] = {"error": f"{type(exc).__name__}: {exc}"}
 
     # ---- other configurations, kernel-only, single GPU
-    if world == 1 and not args.no_others:
+    extras = set() if args.no_others else {e.strip() for e in args.others.split(",") if e.strip()}
+    if world == 1 and extras:
         for name in ("cfg0", "cfg1", "cfg3", "cfg4"):
-            if name == args.workload:
+            if name == args.workload or "configs" not in extras:
                 continue
             try:
                 c = CONFIGS[name]
@@ -654,6 +657,8 @@ def main():
         # The same workload with the layer's skip and gate, (Y + x D) silu(z) of model_ref.py:116-118, fused into the
         # kernel's epilogue, next to the same three steps done as separate PyTorch passes over Y.
         try:
+            if "skip_gate" not in extras:
+                raise KeyError("skipped")
             c = CONFIGS[args.workload]
             sb = algorithmic_bytes(c) + c["b"] * c["s"] * c["h"] * c["p"] * 2   # + one read of z
             ns = min(16, max(2, int(math.ceil(2.5 * L2_BYTES / sb))))
@@ -689,12 +694,16 @@ def main():
                 "ms_per_step_with_pytorch_epilogue": ms_u}
             del ss, oo, zz
             torch.cuda.empty_cache()
+        except KeyError:
+            pass
         except Exception as exc:
             others[args.workload + "+skip_gate"] = {"error": f"{type(exc).__name__}: {exc}"}
 
         # The X producer of the same workload: causal depthwise conv1d(k=4) + SiLU (model_ref.py:83-86) over
         # [b, s, h*p], read as a column slice of a projection-sized buffer; bytes = one read + one write.
         try:
+            if "conv" not in extras:
+                raise KeyError("skipped")
             c = CONFIGS[args.workload]
             dch = c["h"] * c["p"]
             wdt = TDT[c["dtype"]]
@@ -712,14 +721,17 @@ def main():
                                                       "hbm_frac_of_measured": cbytes / (ms_c * 1e-3) / 1e9 / peak}
             del wide, yo
             torch.cuda.empty_cache()
+        except KeyError:
+            pass
         except Exception as exc:
             others[args.workload + ":conv1d_silu"] = {"error": f"{type(exc).__name__}: {exc}"}
 
         # The whole Model (reference contract: Model / get_init_inputs / get_inputs, model_ref.py:165-229) at the
         # reference's production configuration, drop-in next to the reference, timed by the reference's harness.
         try:
-            others["mamba_model_24_layers"] = model_through_reference_harness(dev, args.steps,
-                                                                              with_compile=not args.no_model_compile)
+            if "model" in extras:
+                others["mamba_model_24_layers"] = model_through_reference_harness(
+                    dev, args.steps, with_compile=not args.no_model_compile)
         except Exception as exc:
             others["mamba_model_24_layers"] = {"error": f"{type(exc).__name__}: {exc}"}
             torch.cuda.empty_cache()

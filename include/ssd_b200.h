@@ -94,8 +94,10 @@ typedef struct SsdArgs {
   int32_t dtype;                /* SSD_DTYPE_* of X, B, C, dt, Y */
   int32_t kernel;               /* SSD_KERNEL_* */
   int32_t flags;                /* SSD_FLAG_* */
-  int32_t nsegments;            /* 0 = choose; >0 = split each sequence into this many independently
-                                   scanned segments joined by a state fold (needs workspace) */
+  int32_t nsegments;            /* 0 = choose; 1 = whole sequences; >1 = cut each sequence (needs workspace): into
+                                   this many independently scanned segments joined by a state fold, or, for the
+                                   two-head tensor-core kernel's plain forward, at the points an even deal of
+                                   all tiles over the SMs gives */
   int32_t wait_limit_ms;        /* bound of every device-side wait (a kernel that runs into it writes its code to
                                    `status` and returns); 0 = the default, about one second */
   int64_t x_stride[3];          /* b, s, h */
@@ -129,9 +131,12 @@ size_t ssd_b200_workspace_bytes(const SsdArgs* args);
 const char* ssd_b200_kernel_name(const SsdArgs* args);
 
 /* How ssd_b200_forward() will run these arguments: the resolved SSD_KERNEL_* family, the number of
- * segments each sequence is cut into, and the number of kernel launches it enqueues (1; 3 for the
- * two-pass segmented scan; 1 plus a memset for chained segments).  Any out pointer may be NULL.
- * Returns SSD_OK or the validation error.  No reference counterpart. */
+ * segments each sequence is cut into (2 stands for "cut" where the cut points follow from the grid),
+ * and the number of kernel launches it enqueues: 1 for whole sequences; 1 plus a memset where the
+ * two-head tensor-core kernel deals the tiles of all sequences out evenly inside one launch (states
+ * handed from CTA to CTA, or folded from the pairs each CTA publishes for the last piece of its range);
+ * 3 for the two-pass segmented scan (2 with SSD_FLAG_STATE_ONLY or SSD_FLAG_REUSE_SEGMENTS).  Any out
+ * pointer may be NULL.  Returns SSD_OK or the validation error.  No reference counterpart. */
 int ssd_b200_plan(const SsdArgs* args, int32_t* kernel, int32_t* nsegments, int32_t* launches);
 
 /* (A Z whose address or strides are not multiples of 16 bytes is applied by the stand-alone epilogue kernel.)

@@ -141,3 +141,24 @@ def test_oracle_pieces_equal_the_reference_layer_intermediates(golden_dir):
     Y = O.ssd_chunked(t["x"], t["A_dt"], t["B"], t["C"], block_len, dt=t["dt"])               # :123-162
     assert torch.equal(Y, t["y_core"])
     assert torch.equal(O.ssd_epilogue(Y, t["x"], t["w.D"], t["z"]), t["y_gated"])             # :116-118
+
+
+def test_reference_bytecode_reproduces_the_golden_outputs(golden_dir):
+    """``oracle/_ref`` (the unmodified reference, byte-compiled by ``oracle/build_ref.py`` where the checkout is
+    present) is what the benchmark's CPU arm times: it must give the golden outputs bit for bit."""
+    import numpy as np
+
+    from oracle import build_ref as R
+
+    mod = R.load_model_ref()
+    if mod is None:
+        pytest.skip("oracle/_ref was not built on this machine")
+    assert R.load_ref_bench() is not None
+    for name in ("core_n16_q64", "core_n64_grouped_q32", "core_n128_q128_dt"):
+        z = np.load(golden_dir / f"{name}.npz")
+        d = {k: torch.from_numpy(z[k]) for k in z.files if k != "chunk"}
+        h, g = d["X"].shape[2], d["B"].shape[2]
+        Bh, Ch = d["B"].repeat_interleave(h // g, 2), d["C"].repeat_interleave(h // g, 2)
+        with torch.inference_mode():
+            Y = R.reference_core(mod, d["X"], d["A"], Bh, Ch, int(z["chunk"]), dt=d.get("dt"))
+        assert torch.equal(Y, d["Y"]), name

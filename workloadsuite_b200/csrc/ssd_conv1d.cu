@@ -19,11 +19,12 @@ namespace {
 constexpr int kTokensPerThread = 32;
 constexpr int kMaxTaps = 8;
 
-// pairs of 16-bit elements <-> float2
+// 8 consecutive elements <-> 8 floats, through 16-byte vectors kept in registers when `vec`.
 __device__ __forceinline__ float2 up2(const __half*, uint32_t v) { return __half22float2(*reinterpret_cast<const __half2*>(&v)); }
 __device__ __forceinline__ float2 up2(const __nv_bfloat16*, uint32_t v) {
   return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
 }
+__device__ __forceinline__ float2 up2(const float*, uint32_t) { return make_float2(0.f, 0.f); }   // (never taken)
 __device__ __forceinline__ uint32_t pk2(const __half*, float a, float b) {
   __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
@@ -32,75 +33,56 @@ __device__ __forceinline__ uint32_t pk2(const __nv_bfloat16*, float a, float b) 
   __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
 }
-// V consecutive elements (V = 8: one 16-byte vector of a 16-bit row; V = 4: half of it) <-> V floats.
-template <typename T, int V>
-__device__ __forceinline__ void loadv(const T* p, float (&v)[V], bool vec) {
-  if constexpr (sizeof(T) == 2) {
-    if (!vec) {
-#pragma unroll
-      for (int e = 0; e < V; ++e) v[e] = Cvt<T>::to_f(p[e]);
-      return;
-    }
-    uint32_t q[V / 2];
-    if (V == 8) {
-      const uint4 r = *reinterpret_cast<const uint4*>(p);
-      q[0] = r.x; q[1] = r.y; q[V / 2 - 2] = r.z; q[V / 2 - 1] = r.w;
-    } else {
-      const uint2 r = *reinterpret_cast<const uint2*>(p);
-      q[0] = r.x; q[1] = r.y;
-    }
-#pragma unroll
-    for (int e = 0; e < V / 2; ++e) {
-      const float2 a = up2(p, q[e]);
-      v[2 * e] = a.x; v[2 * e + 1] = a.y;
-    }
-    return;
-  }
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&v)[8], bool vec) {
   if (vec) {
-#pragma unroll
-    for (int e = 0; e < V; e += 4) {
-      const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + e);
-      v[e] = a.x; v[e + 1] = a.y; v[e + 2] = a.z; v[e + 3] = a.w;
-    }
+    const uint4 q = *reinterpret_cast<const uint4*>(p);
+    const float2 a = up2(p, q.x), b = up2(p, q.y), c = up2(p, q.z), d = up2(p, q.w);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
   } else {
 #pragma unroll
-    for (int e = 0; e < V; ++e) v[e] = Cvt<T>::to_f(p[e]);
+    for (int e = 0; e < 8; ++e) v[e] = Cvt<T>::to_f(p[e]);
   }
 }
-template <typename T, int V>
-__device__ __forceinline__ void storev(T* p, const float (&v)[V], bool vec) {
-  if constexpr (sizeof(T) == 2) {
-    if (!vec) {
-#pragma unroll
-      for (int e = 0; e < V; ++e) p[e] = Cvt<T>::from_f(v[e]);
-      return;
-    }
-    uint32_t q[V / 2];
-#pragma unroll
-    for (int e = 0; e < V / 2; ++e) q[e] = pk2(p, v[2 * e], v[2 * e + 1]);
-    if (V == 8) *reinterpret_cast<uint4*>(p) = make_uint4(q[0], q[1], q[V / 2 - 2], q[V / 2 - 1]);
-    else *reinterpret_cast<uint2*>(p) = make_uint2(q[0], q[1]);
-    return;
-  }
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&v)[8], bool vec) {
   if (vec) {
-#pragma unroll
-    for (int e = 0; e < V; e += 4)
-      *reinterpret_cast<float4*>(reinterpret_cast<float*>(p) + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
   } else {
 #pragma unroll
-    for (int e = 0; e < V; ++e) p[e] = Cvt<T>::from_f(v[e]);
+    for (int e = 0; e < 8; ++e) v[e] = p[e];
+  }
+}
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float (&v)[8], bool vec) {
+  if (vec) {
+    uint4 q;
+    q.x = pk2(p, v[0], v[1]); q.y = pk2(p, v[2], v[3]); q.z = pk2(p, v[4], v[5]); q.w = pk2(p, v[6], v[7]);
+    *reinterpret_cast<uint4*>(p) = q;
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) p[e] = Cvt<T>::from_f(v[e]);
+  }
+}
+template <>
+__device__ __forceinline__ void store8<float>(float* p, const float (&v)[8], bool vec) {
+  if (vec) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) p[e] = v[e];
   }
 }
 
-// One thread: V consecutive channels, kTokensPerThread consecutive tokens, the last K-1 rows kept in registers as a
-// sliding window.  V = 4 for 16-bit types (8-byte vectors: a warp still reads 256 contiguous bytes per row) keeps the
-// thread's registers low enough for eight rows in flight per thread on 20 resident warps (40 KB of reads in flight
-// per SM; bandwidth x latency asks for about 35 KB); V = 8 for fp32.
-template <typename T, int K, int V>
-__global__ void __launch_bounds__(128, (V == 4 ? 5 : 4))
+// One thread: 8 consecutive channels (one 16-byte vector of a 16-bit row), kTokensPerThread consecutive tokens,
+// the last K-1 rows kept in registers as a sliding window.
+template <typename T, int K>
+__global__ void __launch_bounds__(128, 4)
 conv1d_silu_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ bias, T* __restrict__ y,
                    int batch, int seqlen, int channels, int64_t xsb, int64_t xsl, int64_t ysb, int64_t ysl, int vec_ok) {
-  const int cvecs = channels / V;
+  const int cvecs = channels / 8;
   const int chunks = (seqlen + kTokensPerThread - 1) / kTokensPerThread;
   const int64_t total = (int64_t)batch * chunks * cvecs;
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -109,22 +91,29 @@ conv1d_silu_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __
   const int64_t r = i / cvecs;
   const int ch = (int)(r % chunks);
   const int b = (int)(r / chunks);
-  const int c0 = V * cv;
+  const int c0 = 8 * cv;
   const int t_begin = ch * kTokensPerThread, t_end = min(seqlen, t_begin + kTokensPerThread);
 
-  float wk[K][V], bs[V];
+  float wk[K][8], bs[8];
 #pragma unroll
-  for (int e = 0; e < V; ++e) {
+  for (int e = 0; e < 8; ++e) {
     bs[e] = bias ? Cvt<T>::to_f(bias[c0 + e]) : 0.f;
 #pragma unroll
     for (int k = 0; k < K; ++k) wk[k][e] = Cvt<T>::to_f(w[(int64_t)(c0 + e) * K + k]);
   }
   const bool vec = vec_ok != 0;
-  const T* xrow = x + b * xsb + c0;
-  auto emit = [&](int t, float (&win)[K][V]) {   // win holds rows t-(K-1) .. t
-    float out[V];
+  auto load_row = [&](int t, float (&v)[8]) {   // zeros outside the sequence
+    if (t < 0 || t >= seqlen) {
 #pragma unroll
-    for (int e = 0; e < V; ++e) {
+      for (int e = 0; e < 8; ++e) v[e] = 0.f;
+    } else {
+      load8<T>(x + b * xsb + (int64_t)t * xsl + c0, v, vec);
+    }
+  };
+  auto emit = [&](int t, float (&win)[K][8]) {   // win holds rows t-(K-1) .. t
+    float out[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
       float acc = bs[e];
 #pragma unroll
       for (int k = 0; k < K; ++k) acc = fmaf(wk[k][e], win[k][e], acc);
@@ -137,45 +126,45 @@ conv1d_silu_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __
         out[e] = __fdividef(acc, 1.f + __expf(-acc));
       }
     }
-    storev<T, V>(y + b * ysb + (int64_t)t * ysl + c0, out, vec);
+    store8<T>(y + b * ysb + (int64_t)t * ysl + c0, out, vec);
   };
 
-  float win[K][V];   // win[k] = row t-(K-1)+k
+  float win[K][8];   // win[k] = row t-(K-1)+k
 #pragma unroll
-  for (int k = 0; k < K - 1; ++k) {   // the K-1 rows before the run: zeros before the sequence start
-    const int t = t_begin - (K - 1) + k;
-    if (t < 0) {
+  for (int k = 0; k < K - 1; ++k) load_row(t_begin - (K - 1) + k, win[k + 1]);
+  if (vec && sizeof(T) == 2) {
+    // rows fetched four at a time as raw 16-byte vectors: several loads per thread in flight, few registers
+    constexpr int kBatch = 4;
+    const T* xrow = x + b * xsb + c0;
+    for (int t0 = t_begin; t0 < t_end; t0 += kBatch) {
+      uint4 raw[kBatch];
 #pragma unroll
-      for (int e = 0; e < V; ++e) win[k + 1][e] = 0.f;
-    } else {
-      loadv<T, V>(xrow + (int64_t)t * xsl, win[k + 1], vec);
-    }
-  }
-  // rows fetched kBatch at a time: several loads per thread in flight before the first is used
-  constexpr int kBatch = (V == 4 ? 8 : 4);
-  for (int t0 = t_begin; t0 < t_end; t0 += kBatch) {
-    float rows[kBatch][V];
+      for (int u = 0; u < kBatch; ++u)
+        raw[u] = (t0 + u < t_end) ? *reinterpret_cast<const uint4*>(xrow + (int64_t)(t0 + u) * xsl) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-    for (int u = 0; u < kBatch; ++u) {
-      if (t0 + u < t_end) {
-        loadv<T, V>(xrow + (int64_t)(t0 + u) * xsl, rows[u], vec);
-      } else {
+      for (int u = 0; u < kBatch; ++u) {
+        if (t0 + u < t_end) {
 #pragma unroll
-        for (int e = 0; e < V; ++e) rows[u][e] = 0.f;
-      }
-    }
+          for (int k = 0; k < K - 1; ++k) {
 #pragma unroll
-    for (int u = 0; u < kBatch; ++u) {
-      if (t0 + u < t_end) {
-#pragma unroll
-        for (int k = 0; k < K - 1; ++k) {
-#pragma unroll
-          for (int e = 0; e < V; ++e) win[k][e] = win[k + 1][e];
+            for (int e = 0; e < 8; ++e) win[k][e] = win[k + 1][e];
+          }
+          const float2 a = up2(xrow, raw[u].x), bq = up2(xrow, raw[u].y), c = up2(xrow, raw[u].z), d = up2(xrow, raw[u].w);
+          win[K - 1][0] = a.x; win[K - 1][1] = a.y; win[K - 1][2] = bq.x; win[K - 1][3] = bq.y;
+          win[K - 1][4] = c.x; win[K - 1][5] = c.y; win[K - 1][6] = d.x; win[K - 1][7] = d.y;
+          emit(t0 + u, win);
         }
-#pragma unroll
-        for (int e = 0; e < V; ++e) win[K - 1][e] = rows[u][e];
-        emit(t0 + u, win);
       }
+    }
+  } else {
+    for (int t = t_begin; t < t_end; ++t) {
+#pragma unroll
+      for (int k = 0; k < K - 1; ++k) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) win[k][e] = win[k + 1][e];
+      }
+      load_row(t, win[K - 1]);
+      emit(t, win);
     }
   }
 }
@@ -183,9 +172,8 @@ conv1d_silu_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __
 template <typename T>
 int launch_conv(const void* x, const void* w, const void* bias, void* y, int batch, int seqlen, int channels, int taps,
                 int64_t xsb, int64_t xsl, int64_t ysb, int64_t ysl, cudaStream_t stream) {
-  constexpr int V = sizeof(T) == 2 ? 4 : 8;
   const int chunks = (seqlen + kTokensPerThread - 1) / kTokensPerThread;
-  const int64_t total = (int64_t)batch * chunks * (channels / V);
+  const int64_t total = (int64_t)batch * chunks * (channels / 8);
   if ((total + 127) / 128 > 0x7fffffffLL) return SSD_ERR_TOO_LARGE;
   const unsigned grid = (unsigned)((total + 127) / 128);
   const int per16 = 16 / (int)sizeof(T);
@@ -196,9 +184,9 @@ int launch_conv(const void* x, const void* w, const void* bias, void* y, int bat
   const T* bb = static_cast<const T*>(bias);
   T* yy = static_cast<T*>(y);
   switch (taps) {
-    case 2: conv1d_silu_kernel<T, 2, V><<<grid, 128, 0, stream>>>(xx, ww, bb, yy, batch, seqlen, channels, xsb, xsl, ysb, ysl, al); break;
-    case 3: conv1d_silu_kernel<T, 3, V><<<grid, 128, 0, stream>>>(xx, ww, bb, yy, batch, seqlen, channels, xsb, xsl, ysb, ysl, al); break;
-    case 4: conv1d_silu_kernel<T, 4, V><<<grid, 128, 0, stream>>>(xx, ww, bb, yy, batch, seqlen, channels, xsb, xsl, ysb, ysl, al); break;
+    case 2: conv1d_silu_kernel<T, 2><<<grid, 128, 0, stream>>>(xx, ww, bb, yy, batch, seqlen, channels, xsb, xsl, ysb, ysl, al); break;
+    case 3: conv1d_silu_kernel<T, 3><<<grid, 128, 0, stream>>>(xx, ww, bb, yy, batch, seqlen, channels, xsb, xsl, ysb, ysl, al); break;
+    case 4: conv1d_silu_kernel<T, 4><<<grid, 128, 0, stream>>>(xx, ww, bb, yy, batch, seqlen, channels, xsb, xsl, ysb, ysl, al); break;
     default: return SSD_ERR_UNSUPPORTED;
   }
   return cudaGetLastError() == cudaSuccess ? SSD_OK : SSD_ERR_CUDA;

@@ -190,6 +190,10 @@ def ssd_forward(
     reference block's own X, ``model_ref.py:83-89``) is first copied into the row layout.
     All tensors must be on X's device.  No host synchronisation.
 
+    ``nsegments``: None lets the library choose; 1 keeps sequences whole; more cuts them (see ``plan``):
+    the tensor-core kernel deals the tiles of all sequences out evenly over the SMs inside one launch, the other
+    kernels scan that many segments in two passes joined by a fold.
+
     A sequence that is cut into segments uses one scratch buffer per device, kept between
     calls and shared by all of them: calls that may overlap on the GPU (different streams)
     must be serialised by the caller, and ``reuse_segments`` relies on no other segmented
