@@ -11,7 +11,9 @@
 // the order the warpgroup runs them inside one loop iteration:
 //   a. H <- exp(cs_last) H + S(k)         (model_ref.py:150,156)   S = B^T.Xd from step c of the previous iteration
 //   e. Y(k-1) -> global                    (:162)                   the P.X MMA of tile k-1 ran under step a
-//   c. tile k+1: prefix sum (:135), Xd = exp(cs_last - cs_l) x~ (:144,148) -> smem -> S MMA
+//   c. tile k+1: prefix sum (:135), Xd = exp(cs_last - cs_l) x~ (:144,148) -> smem -> S MMA; the rows of Xd are dealt
+//      to the four warps unevenly (the row's scale goes through shared memory), the warps with fewer blocks of P in
+//      step d taking more
 //   d. P(k) = G o exp(segsum) o causal     (:139-145) -> TMEM as the A operand of Y += P.X
 //   b. Y(k) <- exp(cs_l) * (C.H)           (:160-161) scaled in place in TMEM (the C.H MMA ran under steps c, d)
 //      16-bit copy of H(k+1) -> smem for the next C.H MMA
@@ -49,7 +51,7 @@ struct Layout2 {
   static constexpr int oXd = oX + 2 * kXStages * kBlk;   // [head]
   static constexpr int oH = oXd + 2 * kBlk;      // [head], N rows of 128 B
   static constexpr int oMisc = oH + 2 * N * 128;
-  static constexpr int kBytes = oMisc + 2560;   // no slack: the dynamic segment must start 1024-byte aligned
+  static constexpr int kBytes = oMisc + 3072;   // no slack: the dynamic segment must start 1024-byte aligned
 };
 
 // Work list of this CTA.
@@ -91,9 +93,10 @@ struct Misc2 {
   // Double-buffered by tile parity: step c writes the next tile's values while step d still reads this tile's.
   alignas(16) float cf[2][2][T];   // [head][parity][row]: exp(cs at the end of the row's 32-block - cs of the row)
   float cend[2][2][4];             // [head][parity][block]: cs * log2(e) at the end of each 32-row block
+  uint16_t xs[2][T];               // [head][row]: the 16-bit scale exp(cs_last - cs_row) * dt of the row of X being turned into Xd
 };
 
-static_assert(sizeof(Misc2) <= 2560, "Misc2 outgrew its shared-memory slot");
+static_assert(sizeof(Misc2) <= 3072, "Misc2 outgrew its shared-memory slot");
 static_assert(Layout2<128>::kBytes <= 232448, "shared memory budget of one SM exceeded");
 
 struct Tc2Params {
@@ -291,6 +294,15 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             tma_load_4d(smem + L::oX + (kXStages * h + st) * kBlk, &tmX, &m->full_x[h][st], 0, w.h0 + h, t0, w.bi);
           }
           if (!ok) break;
+          // B before C: the B tile is free as soon as the previous tile's G and S MMAs are done, the C tile only once
+          // its C.H MMA is, which waits for the read-out of the tile before; the S MMA of this tile must not wait that long.
+          if (it > 0) ok = wait2(&m->empty_b, (it - 1) & 1, m, STATUS_WAIT_TIMEOUT_MMA, status);
+          if (!ok) break;
+          mbar_expect_tx(&m->full_b, NB * kBlk);
+#pragma unroll
+          for (int kb = 0; kb < NB; ++kb)
+            tma_load_4d(smem + L::oB + kb * kBlk, &tmB, &m->full_b, 64 * kb, w.gi, t0, w.bi);
+          if (!ok) break;
           if (w.yflag) {
             if (ity > 0) ok = wait2(&m->empty_c, (ity - 1) & 1, m, STATUS_WAIT_TIMEOUT_MMA, status);
             if (!ok) break;
@@ -300,12 +312,6 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
               tma_load_4d(smem + L::oC + kb * kBlk, &tmC, &m->full_c, 64 * kb, w.gi, t0, w.bi);
             ++ity;
           }
-          if (it > 0) ok = wait2(&m->empty_b, (it - 1) & 1, m, STATUS_WAIT_TIMEOUT_MMA, status);
-          if (!ok) break;
-          mbar_expect_tx(&m->full_b, NB * kBlk);
-#pragma unroll
-          for (int kb = 0; kb < NB; ++kb)
-            tma_load_4d(smem + L::oB + kb * kBlk, &tmB, &m->full_b, 64 * kb, w.gi, t0, w.bi);
         }
       }
       if (m->abort_flag && it > 0) {
@@ -478,7 +484,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     float asum = 0.f, acomp = 0.f;   // compensated (Kahan) sum of the tile totals; FP64 is slow on this part
 
     // prefix sum of the log-decay over the 128 rows (model_ref.py:135); publishes cs*log2(e) for the P step
-    auto scan_tile = [&](float a, float dtv, uint32_t par, bool sync_after, float& cs_o, float& tot_o, float& cs2_o,
+    auto scan_tile = [&](float a, float dtv, uint32_t par, float& cs_o, float& tot_o, float& cs2_o,
                          float& cs2c_o) {
       float v = a;
 #pragma unroll
@@ -497,26 +503,35 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       m->cf[h][par][l] = ex2(__shfl_sync(0xffffffffu, cs2_o, 31) - cs2_o) * dtv;
       cs2c_o = cs2_o - fmaxf(__log2f(dtv), -60.f);
       if (lane == 31) m->cend[h][par][q] = cs2_o;
-      // cf / cend are read one tile later and the warp sums are rewritten one tile later: the barrier of the Y
-      // read-out lies in between, except after an item's first tile and in state-only mode
-      if (sync_after) named_bar_sync(bar_id, 128);
+      // the row's scale for Xd (model_ref.py:144,148), for whichever thread turns that row of X into Xd
+      m->xs[h][l] = (uint16_t)pack2<T16>(ex2((tot_o - cs_o) * kLog2e) * dtv, 0.f);
+      named_bar_sync(bar_id, 128);
     };
-    // Xd = exp(cs_last - cs_l) * dt * x (model_ref.py:144,148) from X stage `st` into this head's Xd buffer
-    auto make_xd = [&](uint32_t st, float cs_t, float tot_t, float dtv) {
-      const float dl = ex2((tot_t - cs_t) * kLog2e) * dtv;
-      const uint32_t xrow = sX + (kXStages * h + st) * kBlk + l * 128, xdrow = sXdh + l * 128;
-      // packed 16-bit arithmetic, as the reference does for X*dt and the decay-scaled X (model_ref.py:144,148)
-      const uint32_t dl2 = pack2<T16>(dl, dl);
-      uint4 rawv[8];
-#pragma unroll
-      for (int c = 0; c < 8; ++c) rawv[c] = lds128(xrow + ((c ^ swz) << 4));   // all loads first: their latencies overlap
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const uint4 raw = rawv[c];
-        uint4 o;
-        o.x = mul2<T16>(raw.x, dl2); o.y = mul2<T16>(raw.y, dl2);
-        o.z = mul2<T16>(raw.z, dl2); o.w = mul2<T16>(raw.w, dl2);
-        sts128(xdrow + ((c ^ swz) << 4), o);
+    // Xd = exp(cs_last - cs_l) * dt * x (model_ref.py:144,148) from X stage `st` into this head's Xd buffer, in packed
+    // 16-bit arithmetic as the reference does it.  The rows are not dealt out evenly: the mask step that follows gives
+    // warp q (rows 32q..32q+31 of the causal P) q + 1 blocks of 32 columns to fill, and the four warps meet at the next
+    // tile's prefix sum, so the warps with fewer mask blocks take more rows here.  Eight lanes share a row (one 16-byte
+    // piece each), a warp moves four rows per instruction ("a quad": 32 quads per tile).
+    auto make_xd = [&](uint32_t st, bool with_mask) {
+      // first quad of warp 0..3 and the end, one byte each: 0 14 24 30 32 when all four warps also update and copy the
+      // state (N = 128), 0 10 18 26 32 when only warps 0 and 1 do
+      constexpr uint64_t kFirst = N == 128 ? 0x201E180E00ull : 0x201A120A00ull;
+      const int qb = with_mask ? (int)((kFirst >> (8 * q)) & 0xff) : 8 * q;
+      const int qe = with_mask ? (int)((kFirst >> (8 * q + 8)) & 0xff) : 8 * q + 8;
+      const uint32_t xb = sX + (kXStages * h + st) * kBlk;
+      const uint32_t sub = (uint32_t)lane >> 3, pc = (uint32_t)lane & 7u;
+#pragma unroll 1
+      for (int qd = qb; qd < qe; qd += 2) {   // (every share is an even number of quads)
+        const uint32_t r0 = 4 * qd + sub, r1 = r0 + 4;
+        const uint32_t o0 = r0 * 128 + ((pc ^ (r0 & 7u)) << 4), o1 = r1 * 128 + ((pc ^ (r1 & 7u)) << 4);
+        const uint4 a0 = lds128(xb + o0), a1 = lds128(xb + o1);
+        const uint32_t s0 = m->xs[h][r0], s1 = m->xs[h][r1];
+        const uint32_t d0 = s0 | (s0 << 16), d1 = s1 | (s1 << 16);
+        uint4 v;
+        v.x = mul2<T16>(a0.x, d0); v.y = mul2<T16>(a0.y, d0); v.z = mul2<T16>(a0.z, d0); v.w = mul2<T16>(a0.w, d0);
+        sts128(sXdh + o0, v);
+        v.x = mul2<T16>(a1.x, d1); v.y = mul2<T16>(a1.y, d1); v.z = mul2<T16>(a1.z, d1); v.w = mul2<T16>(a1.w, d1);
+        sts128(sXdh + o1, v);
       }
     };
     auto store_hb = [&]() {
@@ -754,10 +769,10 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             a_next = Ag[(int64_t)(t0 + 2 * T + l) * sp.as[1]];
             if (Dg) dt_next = Cvt<T16>::to_f(Dg[(int64_t)(t0 + 2 * T + l) * sp.dts[1]]);
           }
-          scan_tile(a, dtv, itn & 1, j < 0 || !wy, cs_n, tot_n, cs2_n, cs2c_n);
+          scan_tile(a, dtv, itn & 1, cs_n, tot_n, cs2_n, cs2c_n);
           ok = cwait(&m->full_x[h][itn % kXStages], (itn / kXStages) & 1, STATUS_WAIT_TIMEOUT_TMA);
           if (!ok) break;
-          make_xd(itn % kXStages, cs_n, tot_n, dtv);
+          make_xd(itn % kXStages, wy);
           fence_proxy_async();
           warp_arrive(&m->bar_xd);
           if (!wy) warp_arrive(&m->empty_x[h][itn % kXStages]);   // nothing else reads X of a state-only item
