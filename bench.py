@@ -64,6 +64,7 @@ WORKLOAD_NAMES = {
     "cfg3": "long-context b1 s131072 h32 p64 n128 chunk256 g1 bf16",
     "cfg4": "short-seqs b256 s512 h48 p64 n64 g8 chunk128 bf16 + initial states",
 }
+SEQ_EXCHANGE = "auto"
 TDT = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
 L2_BYTES = 126e6
 MIN_TIMED_SECONDS = 0.5
@@ -345,7 +346,7 @@ def parity_leg(mode, rank, world, dev, kw):
         s_loc = case["s"] // world
         sl = slice(rank * s_loc, (rank + 1) * s_loc)
         d = {k: v[:, sl].contiguous().to(dev) for k, v in inp.items()}
-        eng = sharded.SequenceShardedSSD()
+        eng = sharded.SequenceShardedSSD(exchange=SEQ_EXCHANGE)
         Yl = eng.forward(d["X"], d["A"], d["B"], d["C"], chunk, **kw)
         cat_dim = 1
     else:
@@ -396,7 +397,7 @@ def build_step(W, sharded, cfg, rank, world, dev, kw, no_graphs, seq_parallel):
                 kernel=W.kernel_name(sets[0]["X"], sets[0]["A"], sets[0]["B"], sets[0]["C"], chunk,
                                      kernel=kw.get("kernel")))
     if seq_parallel:
-        eng = sharded.SequenceShardedSSD(cuda_graphs=not no_graphs)
+        eng = sharded.SequenceShardedSSD(cuda_graphs=not no_graphs, exchange=SEQ_EXCHANGE)
         info["launches"] = eng.launches_per_step(sets[0]["X"], sets[0]["A"], sets[0]["B"], sets[0]["C"], chunk, **kw)
         info["launch_mode"] = eng.launch_mode()
 
@@ -513,6 +514,9 @@ def main():
     ap.add_argument("--no-others", action="store_true")
     ap.add_argument("--others", default="configs,skip_gate,conv,model",
                     help="which single-GPU extras to time: configs, skip_gate, conv, model (comma-separated)")
+    ap.add_argument("--seq-exchange", default="auto", choices=["auto", "peer", "collective"],
+                    help="state exchange of the sequence-sharded forward: this library's peer-memory kernel, "
+                         "torch.distributed's all-gather, or the first when the ranks can map each other's memory")
     ap.add_argument("--no-parity", action="store_true", help="skip the parity leg (profiling runs only)")
     ap.add_argument("--no-model-compile", action="store_true",
                     help="skip the torch.compile variant of the reference Model (about a minute of compilation)")
@@ -527,6 +531,8 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     cfg = CONFIGS[args.workload]
+    global SEQ_EXCHANGE
+    SEQ_EXCHANGE = args.seq_exchange
 
     if args.impl == "reference":
         run_reference(args, cfg, rank, world)
@@ -602,8 +608,37 @@ def main():
             t = torch.tensor([el], device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             el = float(t.item())
+        # What the link alone allows: the same byte counts as two plain pinned copies, one per direction, started
+        # together on two streams with no dependence between them (the pipeline's Y can only leave after its X arrived).
+        copies_ms = None
+        try:
+            nin, nout = int(runner.h2d_bytes), int(runner.d2h_bytes)
+            hin = torch.empty(nin, dtype=torch.uint8).pin_memory()
+            hback = torch.empty(nout, dtype=torch.uint8).pin_memory()
+            din = torch.empty(nin, dtype=torch.uint8, device=dev)
+            dback = torch.empty(nout, dtype=torch.uint8, device=dev)
+            s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+
+            def copies():
+                with torch.cuda.stream(s_in):
+                    din.copy_(hin, non_blocking=True)
+                with torch.cuda.stream(s_out):
+                    hback.copy_(dback, non_blocking=True)
+
+            copies()
+            torch.cuda.synchronize()
+            tc0 = time.perf_counter()
+            for _ in range(args.e2e_steps):
+                copies()
+            torch.cuda.synchronize()
+            copies_ms = (time.perf_counter() - tc0) / args.e2e_steps * 1e3
+            del hin, hback, din, dback
+        except Exception:
+            copies_ms = None
         e2e = {"value": tokens / el, "unit": "tokens/s", "ms_per_step": el * 1e3,
                "h2d_bytes_per_step": runner.h2d_bytes, "d2h_bytes_per_step": runner.d2h_bytes,
+               "copies_alone_ms": copies_ms,
+               "frac_of_copies_alone": (copies_ms / (el * 1e3)) if copies_ms else None,
                "note": "ssd_b200_forward_host: pinned host tensors in, Y back to host, copies inside the timed region"
                + (" (sequence shards run independently: no state exchange on this path)" if seq_parallel else "")}
         del hs, hout, runner
@@ -625,7 +660,8 @@ def main():
             ms3, _, _, blocks3 = time_blocks(step3, info3["nsets"], max(5, args.steps // 2), 3, dist_on, args.min_seconds)
             others[key] = {"tokens_per_s": c3["b"] * c3["s"] / (ms3 * 1e-3), "ms_per_step": ms3, "blocks": len(blocks3),
                            "hbm_frac_of_measured": info3["set_bytes"] / (ms3 * 1e-3) / 1e9 / peak,
-                           "launch": info3["engine"].launch_mode(), "kernel_launches_per_step": info3["launches"],
+                           "launch": info3["engine"].launch_mode(), "exchange": info3["engine"].exchange_mode(),
+                           "kernel_launches_per_step": info3["launches"],
                            "segments_per_sequence": info3["plan"]["nsegments"], "parity": p3,
                            "phases_ms": info3["engine"].phase_times_ms()}
             del s3, o3, step3, info3

@@ -162,6 +162,31 @@ int ssd_b200_fold_states(const float* states, int64_t states_shard_stride, const
                          int64_t logdecay_shard_stride, const float* initial, float* out, int32_t nshards,
                          int32_t rank, int64_t units, int64_t np, void* stream);
 
+/* All-gather of the sequence shards' (state, log-decay) blocks through NVLink peer memory, for one process per
+ * GPU on one node: the exchange step of the sequence-sharded forward as a kernel of this library (plain peer
+ * stores and release/acquire flags at system scope; no multicast, no TMA on peer memory).  The reference has
+ * no sharded path; the blocks exchanged are the operands of ssd_b200_fold_states() above.
+ *   create      allocates this rank's receive buffer [world][slot_bytes] (slot_bytes rounded up to 16) and returns
+ *               an opaque context and an SSD_XCHG_HANDLE_BYTES-byte handle to pass to the other ranks (any
+ *               transport: the Python wrapper uses torch.distributed.all_gather_object);
+ *   connect     opens the other ranks' buffers; `handles` is world handles in rank order (own entry ignored);
+ *   buffer      this rank's receive buffer (device pointer): slot r holds rank r's block after an all_gather;
+ *   all_gather  one kernel launch on `stream`: waits until every rank has entered the same exchange (so the
+ *               previous one has been consumed), writes `send` (bytes <= slot_bytes, multiple of 16, 16-byte
+ *               aligned) into slot `rank` of every rank's buffer, and completes once every rank's block has
+ *               arrived here.  Every rank must call it the same number of times; the exchange counter lives in
+ *               device memory, so a captured launch can be replayed.  A wait longer than wait_limit_ms (0: two
+ *               seconds) writes 7 to *status (device int32, may be NULL) and ends the kernel.
+ *   destroy     closes the peers' buffers and frees this rank's.
+ * Return SSD_OK or an SSD_ERR_* code. */
+#define SSD_XCHG_HANDLE_BYTES 64
+int ssd_b200_xchg_create(size_t slot_bytes, int32_t world, void** ctx_out, void* handle_out);
+int ssd_b200_xchg_connect(void* ctx, const void* handles, int32_t rank);
+void* ssd_b200_xchg_buffer(void* ctx);
+int ssd_b200_xchg_all_gather(void* ctx, const void* send, size_t bytes, int32_t* status, int32_t wait_limit_ms,
+                             void* stream);
+int ssd_b200_xchg_destroy(void* ctx);
+
 /* Causal depthwise conv1d + SiLU, the producer of the core's X: replaces
  *   x = silu(conv1d(x.transpose)[..., :seq_len]).transpose     model_ref.py:83-86
  * (nn.Conv1d(d, d, taps, padding=taps-1, groups=d, bias) of model_ref.py:50-58) without the two

@@ -32,7 +32,10 @@ EXPORTS = (
     "ssd_b200_forward", "ssd_b200_fold_states", "ssd_b200_host_scratch_bytes", "ssd_b200_forward_host",
     "ssd_b200_static_scratch_capacity", "ssd_b200_forward_static_scratch", "ssd_b200_plan",
     "ssd_b200_conv1d_silu", "ssd_b200_dt_prologue",
+    "ssd_b200_xchg_create", "ssd_b200_xchg_connect", "ssd_b200_xchg_buffer", "ssd_b200_xchg_all_gather",
+    "ssd_b200_xchg_destroy",
 )
+XCHG_HANDLE_BYTES = 64
 
 
 class SsdArgs(C.Structure):
@@ -99,6 +102,16 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     lib.ssd_b200_dt_prologue.restype = C.c_int
     lib.ssd_b200_dt_prologue.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                          C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]
+    lib.ssd_b200_xchg_create.restype = C.c_int
+    lib.ssd_b200_xchg_create.argtypes = [C.c_size_t, C.c_int32, C.POINTER(C.c_void_p), C.c_void_p]
+    lib.ssd_b200_xchg_connect.restype = C.c_int
+    lib.ssd_b200_xchg_connect.argtypes = [C.c_void_p, C.c_void_p, C.c_int32]
+    lib.ssd_b200_xchg_buffer.restype = C.c_void_p
+    lib.ssd_b200_xchg_buffer.argtypes = [C.c_void_p]
+    lib.ssd_b200_xchg_all_gather.restype = C.c_int
+    lib.ssd_b200_xchg_all_gather.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_int32, C.c_void_p]
+    lib.ssd_b200_xchg_destroy.restype = C.c_int
+    lib.ssd_b200_xchg_destroy.argtypes = [C.c_void_p]
     got = lib.ssd_b200_abi_version()
     if got != ABI_VERSION:
         raise RuntimeError(f"libssd_b200 ABI version {got}, binding expects {ABI_VERSION}; rebuild the library")

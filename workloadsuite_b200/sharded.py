@@ -83,13 +83,20 @@ class SequenceShardedSSD:
     """
 
     def __init__(self, group: Optional[dist.ProcessGroup] = None, scan_fn: Callable = _cuda_scan,
-                 fold_fn: Callable = _cuda_fold, cuda_graphs: bool = False):
+                 fold_fn: Callable = _cuda_fold, cuda_graphs: bool = False, exchange: str = "auto"):
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         self.scan_fn = scan_fn
         self.fold_fn = fold_fn
         self.cuda_graphs = cuda_graphs
+        # "peer": this library's all-gather kernel over NVLink peer memory (CUDA tensors, one process per GPU of one
+        # node); "collective": torch.distributed's all_gather_into_tensor (NCCL, or gloo for the CPU tests);
+        # "auto": peer when the tensors are on CUDA devices and the ranks can map each other's buffers
+        if exchange not in ("auto", "peer", "collective"):
+            raise ValueError("exchange must be 'auto', 'peer' or 'collective'")
+        self.exchange = exchange
+        self._peer = None
         self._send = None
         self._recv = None
         self._graphs = {}
@@ -97,10 +104,24 @@ class SequenceShardedSSD:
         self._last = None
 
     def _buffers(self, numel: int, device):
-        if self._send is None or self._send.numel() != numel or self._send.device != device:
-            self._send = torch.empty(numel, dtype=torch.float32, device=device)
-            self._recv = torch.empty(self.world * numel, dtype=torch.float32, device=device)
+        slot = (numel + 3) // 4 * 4          # (the peer kernel moves 16-byte pieces)
+        if self._send is None or self._send.numel() != slot or self._send.device != device:
             self._graphs.clear()
+            if self._peer is not None:
+                self._peer.close()
+                self._peer = None
+            self._send = torch.zeros(slot, dtype=torch.float32, device=device)
+            self._recv = None
+            if self.exchange != "collective" and device.type == "cuda" and self.world > 1:
+                from .peer_exchange import PeerExchange
+                try:
+                    self._peer = PeerExchange(numel, group=self.group, device=device)
+                    self._recv = self._peer.recv
+                except RuntimeError:
+                    if self.exchange == "peer":
+                        raise
+            if self._recv is None:
+                self._recv = torch.empty((self.world, slot), dtype=torch.float32, device=device)
         return self._send, self._recv
 
     # phase 1: local scan from zero, final state and summed log-decay only, packed for the exchange
@@ -111,22 +132,31 @@ class SequenceShardedSSD:
         ns, nd = F.numel(), D.numel()
         send, recv = self._buffers(ns + nd, F.device)
         send[:ns].copy_(F.reshape(-1))
-        send[ns:].copy_(D.reshape(-1))
+        send[ns:ns + nd].copy_(D.reshape(-1))
         return (b, h, n, p, ns, nd)
 
     # phase 3: fold the predecessors, then the real scan seeded with the result
     def _phase_seeded(self, X, A, B, C, chunk, dt, initial_states, dims, kw):
         b, h, n, p, ns, nd = dims
-        recv = self._recv.view(self.world, ns + nd)
+        recv = self._recv
         states = recv[:, :ns].unflatten(1, (b, h, n, p))
-        lds = recv[:, ns:].unflatten(1, (b, h))
+        lds = recv[:, ns:ns + nd].unflatten(1, (b, h))
         # (initial_states, the state before token 0 of the whole sequence, is replicated on all ranks)
         h_in = initial_states if self.rank == 0 else self.fold_fn(states, lds, self.rank, initial_states)
         return self.scan_fn(X, A, B, C, chunk, dt=dt, initial_states=h_in, state_only=False, **kw)
 
     def _exchange(self):
-        # phase 2: the only collective -- every rank's (state, log-decay) lands in every rank's own memory
-        dist.all_gather_into_tensor(self._recv, self._send, group=self.group)
+        # phase 2: the only exchange -- every rank's (state, log-decay) lands in every rank's own memory
+        if self._peer is not None:
+            from .ssd import _status_word
+            self._peer.all_gather(self._send, status=_status_word(self._send.device))
+        else:
+            dist.all_gather_into_tensor(self._recv.view(-1), self._send, group=self.group)
+
+    def exchange_mode(self) -> str:
+        if self._send is None:
+            return "not run yet"
+        return "peer-memory kernel (NVLink stores + flags)" if self._peer is not None else "torch.distributed all-gather"
 
     def forward(self, X, A, B, C, chunk, dt=None, initial_states=None, **kw):
         self._last = (X, A, B, C, chunk, dt, initial_states, dict(kw))
@@ -207,27 +237,48 @@ class SequenceShardedSSD:
         return p_state["launches"] + fold + p_seeded["launches"]
 
     def phase_times_ms(self, repeats: int = 10):
-        """CUDA-event times of the phases of the last ``forward`` (eager launches on the current stream, median over
-        ``repeats``, this rank): local state-only scan, exchange, fold + seeded scan.  Collective on every rank."""
+        """CUDA-event times of the phases of the last ``forward`` (this rank, median over ``repeats``): local
+        state-only scan, exchange, fold + seeded scan.  Each phase is captured into a CUDA graph of its own and the
+        three are replayed back to back, so the figures hold device time and one graph launch each, not the Python
+        launch overhead of the eager path (which is several times the kernels' own time here).  Falls back to eager
+        launches when the collective cannot be captured.  Collective on every rank."""
         if getattr(self, "_last", None) is None:
             return None
         X, A, B, C, chunk, dt, initial_states, kw = self._last
         if not X.is_cuda:
             return None
+        dims = self._phase_local(X, A, B, C, chunk, dt, kw)
+        self._exchange()
+        self._phase_seeded(X, A, B, C, chunk, dt, initial_states, dims, kw)
+        torch.cuda.synchronize(X.device)
+        steps = [lambda: self._phase_local(X, A, B, C, chunk, dt, kw), self._exchange,
+                 lambda: self._phase_seeded(X, A, B, C, chunk, dt, initial_states, dims, kw)]
+        how = "eager launches with events between the phases"
+        if self._one_graph is not False:
+            try:
+                cap = torch.cuda.Stream(device=X.device)
+                graphs = []
+                with torch.cuda.stream(cap):
+                    for fn in steps:
+                        g = torch.cuda.CUDAGraph()
+                        with torch.cuda.graph(g, stream=cap):
+                            fn()
+                        graphs.append(g)
+                torch.cuda.synchronize(X.device)
+                steps = [g.replay for g in graphs]
+                how = "one CUDA graph per phase, replayed back to back with events in between"
+            except Exception:
+                torch.cuda.synchronize(X.device)
         ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(repeats)]
         for r in range(repeats):
             dist.barrier(group=self.group)
             ev[r][0].record()
-            dims = self._phase_local(X, A, B, C, chunk, dt, kw)
-            ev[r][1].record()
-            self._exchange()
-            ev[r][2].record()
-            self._phase_seeded(X, A, B, C, chunk, dt, initial_states, dims, kw)
-            ev[r][3].record()
+            for k, fn in enumerate(steps):
+                fn()
+                ev[r][k + 1].record()
         torch.cuda.synchronize(X.device)
         med = lambda i: sorted(e[i].elapsed_time(e[i + 1]) for e in ev)[repeats // 2]
-        return {"local_state_scan": med(0), "all_gather": med(1), "fold_and_seeded_scan": med(2),
-                "note": "eager launches with events between the phases (the timed step replays one graph)"}
+        return {"local_state_scan": med(0), "all_gather": med(1), "fold_and_seeded_scan": med(2), "note": how}
 
 
 def sequence_sharded_forward(X, A, B, C, chunk, group=None, dt=None, initial_states=None, **kw):

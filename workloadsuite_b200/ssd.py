@@ -33,7 +33,8 @@ def _status_word(device) -> torch.Tensor:
 def device_status(device="cuda:0", clear: bool = True) -> int:
     """Synchronises and returns the kernels' status word for ``device`` (0 = fine; 1/2/3 = a bounded
     wait on TMA / tensor-core / intra-CTA synchronisation ran out and the kernel gave up; 6 = the wait for
-    the piece of a sequence handed over by another CTA ran out)."""
+    the piece of a sequence handed over by another CTA ran out; 7 = the peer-memory exchange waited in vain for
+    another rank)."""
     device = torch.device(device)
     st = _status_word(device)
     torch.cuda.synchronize(device)
