@@ -25,7 +25,7 @@ namespace {
 
 constexpr int kMaxWorld = 16;
 constexpr int kThreads = 256;
-constexpr int kChunksPerPeer = 8;
+constexpr int kChunksPerPeer = 16;
 constexpr int32_t kStatusPeerTimeout = 7;
 
 struct XchgDev {

@@ -58,7 +58,7 @@ def _cuda_scan(X, A, B, C, chunk, dt=None, initial_states=None, state_only=False
     if state_only:
         kw = {k: v for k, v in kw.items() if k != "out"}      # (the state-only phase writes no Y)
         return ssd_forward(X, A, B, C, chunk, dt=dt, initial_states=initial_states, state_only=True,
-                           return_logdecay=True, **kw)
+                           return_logdecay=True, **kw)       # (kw may carry out_final_state / out_logdecay)
     # the state-only call that precedes this one left its per-segment states in the workspace
     return ssd_forward(X, A, B, C, chunk, dt=dt, initial_states=initial_states, reuse_segments=True, **kw)
 
@@ -128,11 +128,16 @@ class SequenceShardedSSD:
     def _phase_local(self, X, A, B, C, chunk, dt, kw):
         b, s_loc, h, p = X.shape
         n = B.shape[3]
-        F, D = self.scan_fn(X, A, B, C, chunk, dt=dt, initial_states=None, state_only=True, **kw)
-        ns, nd = F.numel(), D.numel()
-        send, recv = self._buffers(ns + nd, F.device)
-        send[:ns].copy_(F.reshape(-1))
-        send[ns:ns + nd].copy_(D.reshape(-1))
+        ns, nd = b * h * n * p, b * h
+        send, recv = self._buffers(ns + nd, X.device)
+        if self.scan_fn is _cuda_scan:
+            # the kernels write the shard's final state and log-decay sum straight into the send buffer
+            self.scan_fn(X, A, B, C, chunk, dt=dt, initial_states=None, state_only=True,
+                         out_final_state=send[:ns].view(b, h, n, p), out_logdecay=send[ns:ns + nd].view(b, h), **kw)
+        else:
+            F, D = self.scan_fn(X, A, B, C, chunk, dt=dt, initial_states=None, state_only=True, **kw)
+            send[:ns].copy_(F.reshape(-1))
+            send[ns:ns + nd].copy_(D.reshape(-1))
         return (b, h, n, p, ns, nd)
 
     # phase 3: fold the predecessors, then the real scan seeded with the result

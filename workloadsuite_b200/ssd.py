@@ -177,6 +177,8 @@ def ssd_forward(
     separate_epilogue: bool = False,
     wait_limit_ms: int = 0,
     inject_lost_handover: bool = False,
+    out_final_state: Optional[torch.Tensor] = None,
+    out_logdecay: Optional[torch.Tensor] = None,
 ):
     """Mamba-2 SSD forward ``Y = SSD(X, A, B, C)`` on the current CUDA stream.
 
@@ -207,6 +209,8 @@ def ssd_forward(
 
     Returns Y [b,s,h,p] in X's dtype, plus the float32 final state [b,h,n,p] and/or
     the summed log-decay [b,h] when asked.  With ``state_only`` no Y is produced.
+    ``out_final_state`` / ``out_logdecay`` (contiguous float32 tensors of those shapes on X's device, the state
+    16-byte aligned) receive them in place of fresh tensors, e.g. slices of an exchange buffer.
     ``reuse_segments`` tells a segmented two-pass scan that the previous call on this device was the
     ``state_only`` run over the same tensors, so its per-segment states need not be recomputed.
 
@@ -240,8 +244,15 @@ def ssd_forward(
     Y = None
     if not state_only:
         Y = out if out is not None else torch.empty((b, s, h, p), dtype=X.dtype, device=dev)
-    final_state = torch.empty((b, h, n, p), dtype=torch.float32, device=dev) if want_final else None
-    final_ld = torch.empty((b, h), dtype=torch.float32, device=dev) if return_logdecay else None
+    final_state = final_ld = None
+    if want_final:
+        final_state = out_final_state if out_final_state is not None else \
+            torch.empty((b, h, n, p), dtype=torch.float32, device=dev)
+    if return_logdecay:
+        final_ld = out_logdecay if out_logdecay is not None else torch.empty((b, h), dtype=torch.float32, device=dev)
+    for name, t, shape in (("out_final_state", out_final_state, (b, h, n, p)), ("out_logdecay", out_logdecay, (b, h))):
+        if t is not None and (t.shape != shape or t.dtype != torch.float32 or t.device != dev or not t.is_contiguous()):
+            raise ValueError(f"{name} must be a contiguous float32 tensor {list(shape)} on the device of X")
     args = _lib.SsdArgs()
     _fill(args, X, A, B, C_, dt, initial_states, Y, final_state, final_ld, chunk, kernel, nsegments, state_only,
           reuse_segments)
