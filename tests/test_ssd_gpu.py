@@ -271,6 +271,34 @@ def test_state_only_and_logdecay_outputs():
         assert torch.allclose(D.cpu().double(), O.total_logdecay(inp["A"]), rtol=1e-5, atol=1e-6)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_token_by_token_steps_with_a_carried_state_equal_one_forward(dtype):
+    """Decode-style use of the same entry point: one token per call (``chunk`` 1), the state carried from call to
+    call through ``initial_states`` / ``return_final_state`` (the carry of ``model_ref.py:152-157``), against the
+    unsharded float64 recurrence over the whole run of tokens and against one forward over all of them."""
+    W = _ssd()
+    steps = 6
+    inp = O.make_inputs(b=3, s=steps, h=8, p=64, n=128, g=2, dtype=dtype, init=True, seed=23)
+    d = {k: v.to(DEV) for k, v in inp.items()}
+    H = d["initial_states"]
+    ys = []
+    for t in range(steps):
+        sl = slice(t, t + 1)
+        y, H = W.ssd_forward(d["X"][:, sl], d["A"][:, sl], d["B"][:, sl], d["C"][:, sl], 1, initial_states=H,
+                             return_final_state=True)
+        ys.append(y)
+    Y = torch.cat(ys, dim=1).cpu()
+    Yr, Hr = O.ssd_recurrence(inp["X"], inp["A"], inp["B"], inp["C"], initial_states=inp["initial_states"],
+                              return_final_state=True)
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    assert O.error_metrics(Y, Yr)[0] < tol
+    assert float((H.cpu() - Hr.float()).abs().max() / Hr.abs().max()) < 1e-5
+    Y1, H1 = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], 1, initial_states=d["initial_states"], return_final_state=True)
+    assert O.error_metrics(Y1.cpu(), Yr)[0] < tol
+    assert float((H1.cpu() - H.cpu()).abs().max() / Hr.abs().max()) < 1e-5
+    assert W.device_status(DEV) == 0
+
+
 def test_fold_states_matches_oracle():
     W = _ssd()
     gen = torch.Generator().manual_seed(11)
