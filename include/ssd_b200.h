@@ -216,8 +216,9 @@ int ssd_b200_dt_prologue(const void* dt_raw, int64_t stride_b, int64_t stride_l,
  * in `host` are ignored.  `dev_scratch` is a caller-owned DEVICE buffer of at
  * least ssd_b200_host_scratch_bytes() bytes.  Synchronises the host before
  * returning.  `host->status`, when given, is a HOST int32 that receives the device status word; a non-zero
- * word also makes the call return SSD_ERR_DEVICE_WAIT.  Unlike the other entry points this one creates (and
- * destroys) three CUDA streams and a few events per call.  Stands in for calling the reference module with
+ * word also makes the call return SSD_ERR_DEVICE_WAIT.  Unlike the other entry points this one runs on
+ * three CUDA streams of its own (created with their events on the first call per device and kept; calls on one device take
+ * turns).  Stands in for calling the reference module with
  * CPU tensors (bench.py:217-233 builds inputs on the default device and calls Model). */
 size_t ssd_b200_host_scratch_bytes(const SsdArgs* host);
 int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scratch_bytes);

@@ -8,6 +8,7 @@
 // and overlap (PCIe is full duplex).
 #include <algorithm>
 #include <cstring>
+#include <mutex>
 #include <vector>
 
 #include "ssd_common.cuh"
@@ -15,6 +16,15 @@
 namespace {
 
 constexpr int kSlots = 4;
+constexpr int kMaxDevices = 64;
+
+// Streams and events of the host-buffer pipeline, created on first use per device and kept.
+struct Pipe {
+  cudaStream_t st_in = nullptr, st_run = nullptr, st_out = nullptr;
+  std::vector<cudaEvent_t> events;
+};
+Pipe g_pipes[kMaxDevices];
+std::mutex g_pipes_mu[kMaxDevices];
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 int esize(int dtype) { return dtype == SSD_DTYPE_F32 ? 4 : 2; }
@@ -103,15 +113,22 @@ Plan make_plan(const SsdArgs* a) {
   Plan pl{};
   const int e = esize(a->dtype);
   // chunk length: a multiple of the caller's chunk and of the tensor-core tile (128) when the sequence allows,
-  // sized so that the X chunk is at most 24 MiB (measured: with 8 MiB chunks simultaneous copies in both directions
-  // reach 78 GB/s, with 24 MiB 82 GB/s, and the per-chunk kernel chain costs less)
+  // sized so that the X chunk is at most 48 MiB (measured on the 2.7B layer shape, 84 MB of X per batch entry: two chunks
+  // of 42 MB per entry 8.5 ms, chunks of 24 / 28 / 56 / 84 MB 8.9 / 9.0 / 9.1 / 9.0 ms; with 8 MiB chunks the copies
+  // in both directions together reach 78 GB/s, with 24 MiB and more 82-86 GB/s)
   int unit = a->chunk / gcd_int(a->chunk, 128) * 128;
   if (a->seqlen % unit != 0) unit = a->chunk;
   const size_t per_token = (size_t)a->nheads * a->headdim * e;
   const size_t total = per_token * a->seqlen * a->batch;
-  const size_t cap = std::max<size_t>((size_t)1 << 20, std::min<size_t>((size_t)24 << 20, total / 8));
+  const size_t cap = std::max<size_t>((size_t)1 << 20, std::min<size_t>((size_t)48 << 20, total / 8));
+  // ... and a batch entry is cut into equal chunks (no short remainder chunk at the end of every entry)
   long long tokens = (long long)(cap / per_token) / unit * unit;
   tokens = std::max<long long>(unit, std::min<long long>(tokens, a->seqlen));
+  {
+    const long long pieces = (a->seqlen + tokens - 1) / tokens;
+    const long long even = ((a->seqlen + pieces - 1) / pieces + unit - 1) / unit * unit;
+    tokens = std::max<long long>(unit, std::min<long long>(even, tokens));
+  }
   pl.tokens = (int)tokens;
   pl.nchunks = (a->seqlen + pl.tokens - 1) / pl.tokens;
   // short sequences: several whole batch entries (contiguous in host memory) travel and run as one chunk
@@ -185,18 +202,28 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
   int nsets_used = 0;
   const size_t np = (size_t)n * p;
 
-  cudaStream_t st_in = nullptr, st_run = nullptr, st_out = nullptr;
-  std::vector<cudaEvent_t> ev_in(nslices, nullptr), ev_run(nslices, nullptr), ev_out(nslices, nullptr);
   int rc = SSD_OK;
   auto ck = [&](cudaError_t err) { if (err != cudaSuccess && rc == SSD_OK) rc = SSD_ERR_CUDA; };
-  ck(cudaStreamCreateWithFlags(&st_in, cudaStreamNonBlocking));
-  ck(cudaStreamCreateWithFlags(&st_run, cudaStreamNonBlocking));
-  ck(cudaStreamCreateWithFlags(&st_out, cudaStreamNonBlocking));
-  for (int i = 0; i < nslices && rc == SSD_OK; ++i) {
-    ck(cudaEventCreateWithFlags(&ev_in[i], cudaEventDisableTiming));
-    ck(cudaEventCreateWithFlags(&ev_run[i], cudaEventDisableTiming));
-    ck(cudaEventCreateWithFlags(&ev_out[i], cudaEventDisableTiming));
+  // The three streams and the events of the pipeline are kept per device between calls (creating and destroying some
+  // sixty events and three streams costs a few per cent of a 9 ms call); calls on one device take turns.
+  int dev = 0;
+  ck(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return SSD_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_pipes_mu[dev]);
+  Pipe& pipe = g_pipes[dev];
+  if (!pipe.st_in) ck(cudaStreamCreateWithFlags(&pipe.st_in, cudaStreamNonBlocking));
+  if (!pipe.st_run) ck(cudaStreamCreateWithFlags(&pipe.st_run, cudaStreamNonBlocking));
+  if (!pipe.st_out) ck(cudaStreamCreateWithFlags(&pipe.st_out, cudaStreamNonBlocking));
+  while (rc == SSD_OK && (int)pipe.events.size() < 3 * nslices) {
+    cudaEvent_t ev = nullptr;
+    ck(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    if (ev) pipe.events.push_back(ev);
   }
+  if (rc != SSD_OK) return rc;
+  cudaStream_t st_in = pipe.st_in, st_run = pipe.st_run, st_out = pipe.st_out;
+  cudaEvent_t* ev_in = pipe.events.data();
+  cudaEvent_t* ev_run = ev_in + nslices;
+  cudaEvent_t* ev_out = ev_run + nslices;
 
   char* base = static_cast<char*>(dev_scratch);
   char* entry_base = base + kSlots * pl.slot_bytes;
@@ -307,12 +334,6 @@ int ssd_b200_forward_host(const SsdArgs* host, void* dev_scratch, size_t dev_scr
           acc[(size_t)(slices[i].bi + eb) * h + hh] += ld_host[((size_t)i * pl.group + eb) * h + hh];
     for (size_t k = 0; k < acc.size(); ++k) host->final_logdecay[k] = (float)acc[k];
   }
-  for (auto* v : {&ev_in, &ev_run, &ev_out})
-    for (cudaEvent_t ev : *v)
-      if (ev) cudaEventDestroy(ev);
-  if (st_in) cudaStreamDestroy(st_in);
-  if (st_run) cudaStreamDestroy(st_run);
-  if (st_out) cudaStreamDestroy(st_out);
   return rc;
 }
 
