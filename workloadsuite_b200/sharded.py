@@ -158,6 +158,15 @@ class SequenceShardedSSD:
         else:
             dist.all_gather_into_tensor(self._recv.view(-1), self._send, group=self.group)
 
+    def close(self):
+        """Releases the peer-memory exchange buffers (collective: every rank calls it).  Optional: a process that
+        exits leaves the clean-up to the driver."""
+        self._graphs.clear()
+        if self._peer is not None:
+            self._peer.close()
+            self._peer = None
+            self._send = self._recv = None
+
     def exchange_mode(self) -> str:
         if self._send is None:
             return "not run yet"
