@@ -564,6 +564,10 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             const int row = lane_base + 4 * i + (lane >> 3);
             zr[i] = __ldg(reinterpret_cast<const uint4*>(zbase + (int64_t)(y_t0 + row) * sp.zs[1]));
           }
+          // the next tile's gate rows as far as L2 (one row per lane), so that the loads above find them there
+          if (y_t0 + T + lane_base + lane < sp.seqlen)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const T16*>(sp.Z) + y_bi * sp.zs[0] + y_hi * sp.zs[2] +
+                                                         (int64_t)(y_t0 + T + lane_base + lane) * sp.zs[1]));
         }
       }
       if (!cwait(&m->bar_y[h], y_ity & 1, STATUS_WAIT_TIMEOUT_MMA)) return false;
