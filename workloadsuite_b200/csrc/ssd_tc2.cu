@@ -477,7 +477,10 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     // loaded: this row's value as a column of the diagonal mask block is cs2 - log2(dt) (clamped: dt == 0 must not
     // break the chain of per-token factors there; the clamped column then weighs 2^-60, i.e. nothing).
     float cs2c = 0.f;
-    float a_next = 0.f, dt_next = 1.f;   // log-decay / dt of this thread's row in the next tile to be scanned
+    // log-decay / dt of this thread's row in the next tile to be scanned.  dt stays as loaded (16 bits) until the scan uses
+    // it one iteration later: a conversion right behind the load would hold the warp for the whole memory latency.
+    float a_next = 0.f;
+    T16 dt_next = Cvt<T16>::from_f(1.f);
     bool next_prefetched = false;
     bool store_pending = false;    // (thread l == 0) a TMA store of Y is in flight from X stage store_stage
     uint32_t store_stage = 0;
@@ -551,6 +554,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     bool y_pending = false;
     uint32_t y_it = 0, y_ity = 0;
     int y_hi = 0, y_t0 = 0, y_bi = 0;
+    float y_dskip = 0.f;   // (EPI) D of the head whose tile is queued: loaded when the tile is queued, used a tile later
     auto finish_y = [&]() -> bool {
       // (EPI) the gate rows of this warp's 32 tokens, fetched ahead of the wait for the MMA.  Eight lanes read one
       // 128-byte row per load (whole lines), four rows per instruction; the rows reach their threads through the
@@ -588,7 +592,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           // the stage that the Y rows go to; silu(z) = z * (0.5 + 0.5 tanh(z / 2)), the tanh on 16-bit pairs.
           const bool gate = sp.Z != nullptr;
           if (sp.D) {
-            const float dskip = sp.D[y_hi];
+            const float dskip = y_dskip;
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
               const uint4 xr = lds128(ystage + l * 128 + ((c ^ swz) << 4));
@@ -683,7 +687,7 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       acomp = 0.f;
       if (!next_prefetched && w.ntiles > 0) {   // (the first item of this CTA; later items were prefetched during their predecessor)
         a_next = Ag[(int64_t)(w.t_begin + l) * sp.as[1]];
-        dt_next = Dg ? Cvt<T16>::to_f(Dg[(int64_t)(w.t_begin + l) * sp.dts[1]]) : 1.f;
+        dt_next = Dg ? Dg[(int64_t)(w.t_begin + l) * sp.dts[1]] : Cvt<T16>::from_f(1.f);
       }
       next_prefetched = false;
 
@@ -754,8 +758,8 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
               const int hn = wn.h0 + h;
               a_next = sp.A[wn.bi * sp.as[0] + hn * sp.as[2] + (int64_t)(wn.t_begin + l) * sp.as[1]];
               if (sp.dt)
-                dt_next = Cvt<T16>::to_f(static_cast<const T16*>(sp.dt)[wn.bi * sp.dts[0] + hn * sp.dts[2] +
-                                                                         (int64_t)(wn.t_begin + l) * sp.dts[1]]);
+                dt_next = static_cast<const T16*>(sp.dt)[wn.bi * sp.dts[0] + hn * sp.dts[2] +
+                                                          (int64_t)(wn.t_begin + l) * sp.dts[1]];
               next_prefetched = true;
             }
           }
@@ -768,10 +772,10 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         float cs_n = 0.f, tot_n = 0.f, cs2_n = 0.f, cs2c_n = 0.f;
         if (have_next) {
           const uint32_t itn = (j >= 0) ? it + 1 : it;
-          const float a = a_next, dtv = dt_next;
+          const float a = a_next, dtv = Cvt<T16>::to_f(dt_next);
           if (j + 2 < w.ntiles) {
             a_next = Ag[(int64_t)(t0 + 2 * T + l) * sp.as[1]];
-            if (Dg) dt_next = Cvt<T16>::to_f(Dg[(int64_t)(t0 + 2 * T + l) * sp.dts[1]]);
+            if (Dg) dt_next = Dg[(int64_t)(t0 + 2 * T + l) * sp.dts[1]];
           }
           scan_tile(a, dtv, itn & 1, cs_n, tot_n, cs2_n, cs2c_n);
           ok = cwait(&m->full_x[h][itn % kXStages], (itn / kXStages) & 1, STATUS_WAIT_TIMEOUT_TMA);
@@ -976,6 +980,9 @@ ssd_tc2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           if (wy) {
             y_pending = true;
             y_it = it; y_ity = ity; y_hi = hi; y_t0 = t0; y_bi = w.bi;
+            if constexpr (EPI) {
+              if (sp.D) y_dskip = sp.D[hi];
+            }
             ++ity;
           }
           ++it;
