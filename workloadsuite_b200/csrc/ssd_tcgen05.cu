@@ -264,7 +264,9 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     const T16* Dg = sp.dt ? static_cast<const T16*>(sp.dt) + bi * sp.dts[0] + hi * sp.dts[2] : nullptr;
     T16* Yg = want_y ? static_cast<T16*>(sp.Y) + bi * sp.ys[0] + hi * sp.ys[2] : nullptr;
     float a_next = ntiles > 0 ? Ag[(int64_t)(t_begin + l) * sp.as[1]] : 0.f;
-    float dt_next = (Dg && ntiles > 0) ? Cvt<T16>::to_f(Dg[(int64_t)(t_begin + l) * sp.dts[1]]) : 1.f;
+    // (dt stays as loaded until its use one iteration later: a conversion right behind the load would hold the warp
+    //  for the memory latency)
+    T16 dt_next = (Dg && ntiles > 0) ? Dg[(int64_t)(t_begin + l) * sp.dts[1]] : Cvt<T16>::from_f(1.f);
     double asum = 0.0;
     bool ok = true;
     // the outcome of a wait is made uniform over the warp: tcgen05.ld needs the whole warp
@@ -275,10 +277,10 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     for (int i = 0; i < ntiles && ok; ++i) {
       const int t0 = t_begin + i * T;
       const int par = i & 1, st = i & 1, buf = i & 1;
-      const float a = a_next, dtv = dt_next;
+      const float a = a_next, dtv = Cvt<T16>::to_f(dt_next);
       if (i + 1 < ntiles) {
         a_next = Ag[(int64_t)(t0 + T + l) * sp.as[1]];
-        if (Dg) dt_next = Cvt<T16>::to_f(Dg[(int64_t)(t0 + T + l) * sp.dts[1]]);
+        if (Dg) dt_next = Dg[(int64_t)(t0 + T + l) * sp.dts[1]];
       }
       // ---- in-tile inclusive prefix sum of the log-decay (model_ref.py:135)
       float v = a;
