@@ -164,7 +164,7 @@ int ssd_b200_fold_states(const float* states, int64_t states_shard_stride, const
 
 /* All-gather of the sequence shards' (state, log-decay) blocks through NVLink peer memory, for one process per
  * GPU on one node: the exchange step of the sequence-sharded forward as a kernel of this library (plain peer
- * stores and release/acquire flags at system scope; no multicast, no TMA on peer memory).  The reference has
+ * stores and release/acquire flags at system scope, nothing else touches peer memory).  The reference has
  * no sharded path; the blocks exchanged are the operands of ssd_b200_fold_states() above.
  *   create      allocates this rank's receive buffer [world][slot_bytes] (slot_bytes rounded up to 16) and returns
  *               an opaque context and an SSD_XCHG_HANDLE_BYTES-byte handle to pass to the other ranks (any

@@ -6,7 +6,7 @@
 //   1. tells every peer "I have entered exchange e" (so what a peer wrote for exchange e-1 has been consumed here:
 //      the consumers run before this kernel in stream order),
 //   2. waits for a peer's entry flag, then writes this rank's block into its own slot of that peer's buffer with
-//      plain 16-byte stores (no TMA, no multicast),
+//      plain 16-byte stores (ordinary st.global to the mapped peer buffer, nothing else),
 //   3. publishes "data of rank r for exchange e" on every peer (release at system scope) once all blocks of the
 //      grid have finished their stores, and
 //   4. waits until every rank's data flag for exchange e is set here (acquire at system scope).
