@@ -512,8 +512,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-others", action="store_true")
-    ap.add_argument("--others", default="configs,skip_gate,conv,model",
-                    help="which single-GPU extras to time: configs, skip_gate, conv, model (comma-separated)")
+    ap.add_argument("--others", default="configs,skip_gate,conv,step,model",
+                    help="which single-GPU extras to time: configs, skip_gate, conv, step, model (comma-separated)")
     ap.add_argument("--seq-exchange", default="auto", choices=["auto", "peer", "collective"],
                     help="state exchange of the sequence-sharded forward: this library's peer-memory kernel, "
                          "torch.distributed's all-gather, or the first when the ranks can map each other's memory")
@@ -761,6 +761,38 @@ def main():
             pass
         except Exception as exc:
             others[args.workload + ":conv1d_silu"] = {"error": f"{type(exc).__name__}: {exc}"}
+
+        # Decode-style use: one token per call with the state carried in place (the carry of model_ref.py:152-157), at
+        # the reference's production layer shape.  Bytes = the fp32 state read and written once (+ x, y, z, B, C).
+        try:
+            if "step" not in extras:
+                raise KeyError("skipped")
+            sb_, sh_, sn_, sg_, sdt = 8, 128, 128, 8, torch.float16
+            nst = 6                                  # 6 x 67 MB of state: more than L2 between repeats
+            stt = [torch.randn(sb_, sh_, sn_, 64, device=dev) for _ in range(nst)]
+            xs_ = torch.randn(sb_, sh_, 64, device=dev, dtype=sdt)
+            zs_ = torch.randn(sb_, sh_, 64, device=dev, dtype=sdt)
+            Bs_ = torch.randn(sb_, sg_, sn_, device=dev, dtype=sdt)
+            Cs_ = torch.randn(sb_, sg_, sn_, device=dev, dtype=sdt)
+            dts_ = (0.01 + 0.1 * torch.rand(sb_, sh_, device=dev)).to(sdt)
+            as_ = -torch.rand(sb_, sh_, device=dev)
+            Ds_ = torch.ones(sh_, device=dev)
+            ys_ = torch.empty_like(xs_)
+
+            def st_step(i):
+                W.ssd_step(xs_, as_, Bs_, Cs_, stt[i], dt=dts_, D=Ds_, z=zs_, out=ys_)
+
+            ms_t, _, _, _ = time_blocks(st_step, nst, max(5, args.steps // 2), 3, False, args.min_seconds / 4)
+            tbytes = 2 * stt[0].numel() * 4 + 3 * xs_.numel() * 2 + 2 * Bs_.numel() * 2
+            others["decode_step_b8_h128_n128"] = {"ms_per_step": ms_t, "GBps": tbytes / (ms_t * 1e-3) / 1e9,
+                                                   "hbm_frac_of_measured": tbytes / (ms_t * 1e-3) / 1e9 / peak,
+                                                   "note": "ssd_step: one token, fp32 state [8,128,128,64] updated in place"}
+            del stt
+            torch.cuda.empty_cache()
+        except KeyError:
+            pass
+        except Exception as exc:
+            others["decode_step_b8_h128_n128"] = {"error": f"{type(exc).__name__}: {exc}"}
 
         # The whole Model (reference contract: Model / get_init_inputs / get_inputs, model_ref.py:165-229) at the
         # reference's production configuration, drop-in next to the reference, timed by the reference's harness.

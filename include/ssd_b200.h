@@ -209,6 +209,18 @@ int ssd_b200_dt_prologue(const void* dt_raw, int64_t stride_b, int64_t stride_l,
                          const float* A_log, void* dt_out, float* A_dt_out, int32_t batch, int32_t seqlen,
                          int32_t nheads, int32_t dtype, void* stream);
 
+/* One token of the recurrence with the state carried in place (decode-style use; the reference has only the chunked
+ * forward, whose carry model_ref.py:152-157 reduces to this for a single token):
+ *   state[b,h] <- exp(a[b,h]) * state[b,h] + B[b,g] (x) (dt[b,h] * x[b,h]);   y[b,h] = C[b,g] . state[b,h]
+ * then, when given, y <- (y + x * D[h]) * silu(z)   (model_ref.py:116-118).
+ * x, y, z are [batch, nheads, headdim], B and C [batch, ngroups, dstate], dt [batch, nheads] (NULL: x is already
+ * scaled) in `dtype`, all contiguous; a [batch, nheads] is the token's fp32 log-decay (the reference's A_dt); D [nheads]
+ * fp32 or NULL; state [batch, nheads, dstate, headdim] fp32, 16-byte aligned, updated in place (the layout of
+ * SsdArgs.initial_state / final_state).  headdim == 64, dstate a multiple of 16 up to 256.  HBM-bound on the state. */
+int ssd_b200_step(const void* x, const float* a, const void* B, const void* C, const void* dt, const float* D,
+                  const void* z, float* state, void* y, int32_t batch, int32_t nheads, int32_t headdim,
+                  int32_t dstate, int32_t ngroups, int32_t dtype, void* stream);
+
 /* Whole forward with HOST buffers: copies X/A/B/C (and dt, initial_state when
  * given) from host memory, runs the forward and copies Y (and final_state) back,
  * pipelined over batch slices on internal streams.  Every pointer in `host` is a

@@ -299,6 +299,39 @@ def test_token_by_token_steps_with_a_carried_state_equal_one_forward(dtype):
     assert W.device_status(DEV) == 0
 
 
+@pytest.mark.parametrize("dtype,n,g,epi", [(torch.bfloat16, 128, 2, True), (torch.float16, 64, 1, False),
+                                           (torch.float32, 16, 4, True)])
+def test_step_kernel_equals_the_recurrence_and_the_forward(dtype, n, g, epi):
+    """``ssd_step`` token by token (state carried in place) against the float64 recurrence over the whole run of
+    tokens, and against ``ssd_forward`` over the same tokens; with the layer's skip and gate in one of the cases."""
+    W = _ssd()
+    steps, b, h = 5, 3, 8
+    inp = O.make_inputs(b=b, s=steps, h=h, p=64, n=n, g=g, dtype=dtype, init=True, seed=31, decay_scale=0.3)
+    gen = torch.Generator().manual_seed(32)
+    dt = (0.05 + torch.rand(b, steps, h, generator=gen)).to(dtype)
+    D = torch.randn(h, generator=gen) if epi else None
+    z = torch.randn(b, steps, h, 64, generator=gen).to(dtype) if epi else None
+    d = _to_dev(inp)
+    state = d["initial_states"].clone()
+    ys = []
+    for t in range(steps):
+        ys.append(W.ssd_step(d["X"][:, t], d["A"][:, t], d["B"][:, t], d["C"][:, t], state, dt=dt[:, t].to(DEV),
+                             D=None if D is None else D.to(DEV), z=None if z is None else z[:, t].to(DEV)))
+    Y = torch.stack(ys, dim=1).cpu()
+    Yr, Hr = O.ssd_recurrence(inp["X"], inp["A"], inp["B"], inp["C"], dt=dt, initial_states=inp["initial_states"],
+                              return_final_state=True)
+    if epi:
+        Yr = O.ssd_epilogue(Yr, inp["X"].double(), D.double(), z.double(), dtype=torch.float64)
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    assert max(O.error_metrics(Y, Yr)) < tol
+    assert float((state.cpu().double() - Hr).abs().max() / Hr.abs().max()) < (1e-5 if dtype == torch.float32 else 5e-3)
+    Yf, Hf = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], 1, dt=dt.to(DEV), initial_states=d["initial_states"],
+                           return_final_state=True, D=None if D is None else D.to(DEV),
+                           z=None if z is None else z.to(DEV))
+    assert max(O.error_metrics(Y, Yf.cpu().double())) < tol
+    assert float((state - Hf).abs().max() / Hf.abs().max()) < 5e-3
+
+
 def test_fold_states_matches_oracle():
     W = _ssd()
     gen = torch.Generator().manual_seed(11)

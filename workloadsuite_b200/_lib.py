@@ -33,7 +33,7 @@ EXPORTS = (
     "ssd_b200_static_scratch_capacity", "ssd_b200_forward_static_scratch", "ssd_b200_plan",
     "ssd_b200_conv1d_silu", "ssd_b200_dt_prologue",
     "ssd_b200_xchg_create", "ssd_b200_xchg_connect", "ssd_b200_xchg_buffer", "ssd_b200_xchg_all_gather",
-    "ssd_b200_xchg_destroy",
+    "ssd_b200_xchg_destroy", "ssd_b200_step",
 )
 XCHG_HANDLE_BYTES = 64
 
@@ -102,6 +102,8 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     lib.ssd_b200_dt_prologue.restype = C.c_int
     lib.ssd_b200_dt_prologue.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                          C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]
+    lib.ssd_b200_step.restype = C.c_int
+    lib.ssd_b200_step.argtypes = [C.c_void_p] * 9 + [C.c_int32] * 6 + [C.c_void_p]
     lib.ssd_b200_xchg_create.restype = C.c_int
     lib.ssd_b200_xchg_create.argtypes = [C.c_size_t, C.c_int32, C.POINTER(C.c_void_p), C.c_void_p]
     lib.ssd_b200_xchg_connect.restype = C.c_int

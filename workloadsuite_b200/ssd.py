@@ -346,6 +346,56 @@ def dt_prologue(dt_raw: torch.Tensor, dt_bias: Optional[torch.Tensor], A_log: to
     return dt, A_dt
 
 
+def ssd_step(x: torch.Tensor, a: torch.Tensor, B: torch.Tensor, C_: torch.Tensor, state: torch.Tensor,
+             dt: Optional[torch.Tensor] = None, D: Optional[torch.Tensor] = None, z: Optional[torch.Tensor] = None,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token of the recurrence on the current CUDA stream, ``state`` updated in place (decode-style use of the carry
+    of ``model_ref.py:152-157``): ``state <- exp(a) state + B (x) (dt x)``, ``y = C . state``, then the layer's skip and
+    gate (``model_ref.py:116-118``) when ``D`` / ``z`` are given.
+
+    x [b,h,p] (p = 64), a [b,h] float32 (the token's ``A_dt``), B and C [b,g,n], dt [b,h] or None, D [h], z [b,h,p],
+    state float32 [b,h,n,p] (what ``ssd_forward(..., return_final_state=True)`` returns).  Returns y [b,h,p].
+    Equal, within the kernels' tolerances, to ``ssd_forward`` over a one-token sequence with ``initial_states=state``.
+    """
+    if not x.is_cuda:
+        raise RuntimeError("ssd_step needs CUDA tensors (there is no CPU path)")
+    if x.dim() != 3 or B.dim() != 3 or state.dim() != 4 or x.dtype not in _DTYPES:
+        raise ValueError("expected x [b,h,p], B/C [b,g,n], state [b,h,n,p]")
+    b, h, p = x.shape
+    g, n = B.shape[1], B.shape[2]
+    _same_device(x, a=a, B=B, C=C_, state=state, dt=dt, D=D, z=z, out=out)
+    if h % g != 0:
+        raise ValueError("n_heads must be divisible by n_groups")
+    if (a.shape != (b, h) or a.dtype != torch.float32 or B.shape != (b, g, n) or C_.shape != (b, g, n)
+            or B.dtype != x.dtype or C_.dtype != x.dtype or state.shape != (b, h, n, p) or state.dtype != torch.float32
+            or not state.is_contiguous()):
+        raise ValueError("a must be float32 [b,h], B/C [b,g,n] in x's dtype, state contiguous float32 [b,h,n,p]")
+    if dt is not None and (dt.shape != (b, h) or dt.dtype != x.dtype):
+        raise ValueError("dt must be [b,h] in x's dtype")
+    if z is not None and (z.shape != x.shape or z.dtype != x.dtype):
+        raise ValueError("z must be [b,h,p] in x's dtype")
+    if D is not None:
+        if D.shape != (h,):
+            raise ValueError("D must be [h]")
+        D = D.to(dtype=torch.float32).contiguous()
+    x, a, B, C_ = x.contiguous(), a.contiguous(), B.contiguous(), C_.contiguous()
+    dt = None if dt is None else dt.contiguous()
+    z = None if z is None else z.contiguous()
+    if out is None:
+        out = torch.empty((b, h, p), dtype=x.dtype, device=x.device)
+    elif out.shape != (b, h, p) or out.dtype != x.dtype or not out.is_contiguous():
+        raise ValueError("out must be a contiguous [b,h,p] tensor in x's dtype")
+    ptr = lambda t: None if t is None else t.data_ptr()
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        rc = lib.ssd_b200_step(ptr(x), ptr(a), ptr(B), ptr(C_), ptr(dt), ptr(D), ptr(z), ptr(state), ptr(out),
+                               b, h, p, n, g, _DTYPES[x.dtype],
+                               C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream))
+    if rc != _lib.SSD_OK:
+        _raise(rc)
+    return out
+
+
 def kernel_name(X, A, B, C_, chunk, kernel=None) -> str:
     """Which kernel family ``ssd_forward`` would run for these tensors."""
     _check(X, A, B, C_, None, None)
