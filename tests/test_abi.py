@@ -64,6 +64,34 @@ def test_kernel_choice_and_workspace_queries(lib):
     assert lib.ssd_b200_fold_states(None, 0, None, 0, None, None, 2, 1, 4, 4, None) == -1
 
 
+def test_step_and_exchange_entry_points_reject_bad_arguments_on_the_host(lib):
+    """No device is touched: every call returns before a launch (the pointers are made-up numbers)."""
+    P = 0x10000
+    step = lambda *a: lib.ssd_b200_step(*a)
+    ok_shape = (2, 8, 64, 128, 2, _lib.DTYPE_BF16, None)
+    assert step(None, P, P, P, None, None, None, P, P, *ok_shape) == -1                      # x missing
+    assert step(P, P, P, P, None, None, None, P, P, 2, 8, 64, 128, 3, _lib.DTYPE_BF16, None) == -2    # heads % groups
+    assert step(P, P, P, P, None, None, None, P, P, 2, 8, 32, 128, 2, _lib.DTYPE_BF16, None) == -4    # head dim
+    assert step(P, P, P, P, None, None, None, P, P, 2, 8, 64, 100, 2, _lib.DTYPE_BF16, None) == -4    # state size
+    assert step(P, P, P, P, None, None, None, P + 4, P, *ok_shape) == -7                     # state alignment
+    ctx = C.c_void_p()
+    handle = (C.c_ubyte * _lib.XCHG_HANDLE_BYTES)()
+    assert lib.ssd_b200_xchg_create(1024, 2, None, handle) == -1
+    assert lib.ssd_b200_xchg_create(1024, 0, C.byref(ctx), handle) == -2
+    assert lib.ssd_b200_xchg_create(0, 2, C.byref(ctx), handle) == -2
+    assert lib.ssd_b200_xchg_buffer(None) is None
+    assert lib.ssd_b200_xchg_all_gather(None, P, 1024, None, 0, None) == -2
+
+
+def test_python_wrappers_refuse_cpu_tensors():
+    import torch
+    import workloadsuite_b200 as W
+
+    x = torch.zeros(1, 2, 64)
+    with pytest.raises(RuntimeError):
+        W.ssd_step(x, torch.zeros(1, 2), torch.zeros(1, 1, 16), torch.zeros(1, 1, 16), torch.zeros(1, 2, 16, 64))
+
+
 def test_misaligned_states_and_bad_wait_limit_are_rejected_on_the_host(lib):
     """The tensor-core kernels move the fp32 states as 16-byte vectors: a state pointer that is only 4-byte aligned
     must come back as an error code (explicit kernel) or take the fp32 scan (automatic choice), never reach a
