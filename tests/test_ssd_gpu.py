@@ -300,7 +300,8 @@ def test_token_by_token_steps_with_a_carried_state_equal_one_forward(dtype):
 
 
 @pytest.mark.parametrize("dtype,n,g,epi", [(torch.bfloat16, 128, 2, True), (torch.float16, 64, 1, False),
-                                           (torch.float32, 16, 4, True)])
+                                           (torch.float32, 16, 4, True), (torch.bfloat16, 256, 8, False),
+                                           (torch.float16, 32, 2, True)])
 def test_step_kernel_equals_the_recurrence_and_the_forward(dtype, n, g, epi):
     """``ssd_step`` token by token (state carried in place) against the float64 recurrence over the whole run of
     tokens, and against ``ssd_forward`` over the same tokens; with the layer's skip and gate in one of the cases."""
@@ -325,9 +326,12 @@ def test_step_kernel_equals_the_recurrence_and_the_forward(dtype, n, g, epi):
     tol = 1e-4 if dtype == torch.float32 else 2e-2
     assert max(O.error_metrics(Y, Yr)) < tol
     assert float((state.cpu().double() - Hr).abs().max() / Hr.abs().max()) < (1e-5 if dtype == torch.float32 else 5e-3)
-    Yf, Hf = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], 1, dt=dt.to(DEV), initial_states=d["initial_states"],
-                           return_final_state=True, D=None if D is None else D.to(DEV),
-                           z=None if z is None else z.to(DEV))
+    try:
+        Yf, Hf = W.ssd_forward(d["X"], d["A"], d["B"], d["C"], 1, dt=dt.to(DEV), initial_states=d["initial_states"],
+                               return_final_state=True, D=None if D is None else D.to(DEV),
+                               z=None if z is None else z.to(DEV))
+    except NotImplementedError:      # (a state size only the step kernel covers)
+        return
     assert max(O.error_metrics(Y, Yf.cpu().double())) < tol
     assert float((state - Hf).abs().max() / Hf.abs().max()) < 5e-3
 
